@@ -1,0 +1,244 @@
+/*
+ * abi.cu - the extern "C" surface of libffn_int4.so (declared in include/ffn_int4.h): argument
+ * validation in the reference's order, status codes instead of exceptions, and the reference's
+ * kernel test bridge names.
+ */
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ffn {
+
+static thread_local char g_error[512];
+
+int fail(int status, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+void clear_error() { g_error[0] = '\0'; }
+
+/* Validation shared by the GEMM entry points; mirrors gemm_int4_bf16's checks
+ * (csrc/kernels/gemm_quant.cu:208-224).  Returns 1 for "nothing to do". */
+static int check_gemm(const char *who, const void *a, const void *packed, const void *scales,
+                      const void *out, int M, int N, int K, int group) {
+    if (M < 0 || N < 0 || K <= 0 || group <= 0)
+        return fail(FFN_ERR_CONFIG, "%s: negative extent or nonpositive group", who);
+    if (M == 0 || N == 0) return 1;
+    if (!a || !packed || !scales || !out) return fail(FFN_ERR_CONFIG, "%s: null buffer", who);
+    if (K % group != 0)
+        return fail(FFN_ERR_CONFIG, "%s: K=%d is not a whole number of %d-wide groups", who, K, group);
+    if (group != FFN_INT4_GROUP)
+        return fail(FFN_ERR_CONFIG, "%s: this format's group is %d, not %d", who, FFN_INT4_GROUP, group);
+    if (((uintptr_t)packed & 15) || ((uintptr_t)a & 15))
+        return fail(FFN_ERR_CONFIG, "%s: the activation and the packed weight must be 16-byte aligned", who);
+    return FFN_OK;
+}
+
+static int mlp_common(cudaStream_t stream, const void *normed, void *ws, void *layer_out,
+                      const FfnMlpWeights *w, int tokens, const FfnModelDims *dims) {
+    const int H = dims->hidden_size, I = dims->intermediate_size;
+    uint16_t *base = (uint16_t *)ws;
+    uint16_t *packed_act = base + (size_t)tokens * H;            /* [T, 2I] gate|up */
+    uint16_t *act = packed_act + (size_t)2 * tokens * I;         /* [T, I] */
+    int st = fused_ffn_try(stream, normed, act, layer_out, w, tokens, H, I);
+    if (st != FFN_NOT_ADMITTED) return st;
+    st = gemm_int4_generic(normed, w->gate_up_i4, w->gate_up_i4_scales, packed_act, nullptr, tokens,
+                           2 * I, H, stream);
+    if (st) return st;
+    st = silu_mul_packed(act, packed_act, tokens, I, stream);
+    if (st) return st;
+    return gemm_int4_generic(act, w->down_i4, w->down_i4_scales, layer_out, nullptr, tokens, H, I,
+                             stream);
+}
+
+static int check_mlp(const char *who, const void *in, const void *ws, const void *layer_out,
+                     const FfnMlpWeights *w, int tokens, const FfnModelDims *dims) {
+    if (!dims || !w) return fail(FFN_ERR_CONFIG, "%s: null weights or dims", who);
+    const int limit = dims->max_chunk > 0 ? dims->max_chunk : 128; /* ENGINE_MAX_CHUNK, layers.h:51 */
+    if (tokens < 1 || tokens > limit)
+        return fail(FFN_ERR_CONFIG, "%s: Layer token count exceeds the model's max_chunk", who);
+    if (!in || !ws || !layer_out) return fail(FFN_ERR_CONFIG, "%s: null buffer", who);
+    if (!w->gate_up_i4 || !w->gate_up_i4_scales || !w->down_i4 || !w->down_i4_scales)
+        return fail(FFN_ERR_CONFIG, "%s: the layer carries no INT4 operands (this library has no BF16 path)", who);
+    if (w->i4_group != FFN_INT4_GROUP)
+        return fail(FFN_ERR_CONFIG, "%s: this format's group is %d, not %d", who, FFN_INT4_GROUP, w->i4_group);
+    const int H = dims->hidden_size, I = dims->intermediate_size;
+    if (H <= 0 || I <= 0 || H % FFN_INT4_GROUP || I % FFN_INT4_GROUP)
+        return fail(FFN_ERR_CONFIG, "%s: hidden=%d / intermediate=%d are not whole numbers of %d-wide groups",
+                    who, H, I, FFN_INT4_GROUP);
+    return FFN_OK;
+}
+
+/* A host-or-device pointer made device-resident for the synchronous test bridge. */
+struct Staged {
+    void *dev = nullptr;
+    void *host = nullptr;
+    size_t bytes = 0;
+    bool owned = false;
+    bool writeback = false;
+    int acquire(const void *p, size_t n, bool is_output) {
+        bytes = n;
+        cudaPointerAttributes attr;
+        cudaError_t e = cudaPointerGetAttributes(&attr, p);
+        if (e != cudaSuccess) { (void)cudaGetLastError(); attr.type = cudaMemoryTypeUnregistered; }
+        if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) {
+            dev = const_cast<void *>(p);
+            return FFN_OK;
+        }
+        host = const_cast<void *>(p);
+        owned = true;
+        writeback = is_output;
+        if (cudaMalloc(&dev, n ? n : 1) != cudaSuccess) return fail(FFN_ERR_ALLOC, "test bridge: cudaMalloc(%zu) failed", n);
+        if (!is_output) FFN_CUDA_TRY(cudaMemcpy(dev, p, n, cudaMemcpyHostToDevice), "test bridge: upload");
+        return FFN_OK;
+    }
+    int finish() {
+        if (owned && writeback) FFN_CUDA_TRY(cudaMemcpy(host, dev, bytes, cudaMemcpyDeviceToHost), "test bridge: download");
+        return FFN_OK;
+    }
+    ~Staged() { if (owned && dev) cudaFree(dev); }
+};
+
+}  // namespace ffn
+
+using namespace ffn;
+
+extern "C" {
+
+const char *ffn_int4_last_error(void) { return g_error; }
+int ffn_int4_abi_version(void) { return FFN_INT4_ABI_VERSION; }
+
+int ffn_gemm_int4_bf16(const void *a, const void *packed, const void *scales, void *out, int M, int N,
+                       int K, int group, void *stream) {
+    clear_error();
+    const int c = check_gemm("ffn_gemm_int4_bf16", a, packed, scales, out, M, N, K, group);
+    if (c == 1) return FFN_OK;
+    if (c) return c;
+    return gemm_int4_dispatch(a, packed, scales, out, M, N, K, (cudaStream_t)stream);
+}
+
+int ffn_silu_mul_packed(void *out, const void *packed, int tokens, int intermediate, void *stream) {
+    clear_error();
+    if (tokens < 0 || intermediate < 0) return fail(FFN_ERR_CONFIG, "ffn_silu_mul_packed: negative extent");
+    if (tokens == 0 || intermediate == 0) return FFN_OK;
+    if (!out || !packed) return fail(FFN_ERR_CONFIG, "ffn_silu_mul_packed: null buffer");
+    return silu_mul_packed(out, packed, tokens, intermediate, (cudaStream_t)stream);
+}
+
+int ffn_gemma_rms_norm(void *out, const void *x, const void *weight, int cols, int rows, float eps,
+                       void *stream) {
+    clear_error();
+    if (rows < 0 || cols <= 0 || !(eps > 0.0f) || !(eps < 3.0e38f))
+        return fail(FFN_ERR_CONFIG, "ffn_gemma_rms_norm: invalid shape or epsilon");
+    if (rows == 0) return FFN_OK;
+    if (!out || !x || !weight) return fail(FFN_ERR_CONFIG, "ffn_gemma_rms_norm: null buffer");
+    return gemma_rms_norm(out, x, weight, cols, rows, eps, 1, (cudaStream_t)stream);
+}
+
+int ffn_residual_add(void *dst, const void *src, int n, void *stream) {
+    clear_error();
+    if (n < 0) return fail(FFN_ERR_CONFIG, "ffn_residual_add: negative element count");
+    if (n == 0) return FFN_OK;
+    if (!dst || !src) return fail(FFN_ERR_CONFIG, "ffn_residual_add: null buffer");
+    return residual_add(dst, src, n, (cudaStream_t)stream);
+}
+
+int ffn_dequantize_int4(void *out, const void *packed, const void *scales, int N, int K, int *bad,
+                        void *stream) {
+    clear_error();
+    if (N <= 0 || K <= 0 || K % FFN_INT4_GROUP)
+        return fail(FFN_ERR_CONFIG, "ffn_dequantize_int4: the format cannot hold [%d, %d]", N, K);
+    if (!out || !packed || !scales) return fail(FFN_ERR_CONFIG, "ffn_dequantize_int4: null buffer");
+    return dequantize_int4(out, packed, scales, N, K, bad, (cudaStream_t)stream);
+}
+
+int ffn_forward_mlp(void *cublas, void *stream, const void *residual, void *ws, void *layer_out,
+                    const FfnMlpWeights *w, int tokens, const FfnModelDims *dims) {
+    (void)cublas;
+    clear_error();
+    const int c = check_mlp("ffn_forward_mlp", residual, ws, layer_out, w, tokens, dims);
+    if (c) return c;
+    const void *normed = residual;
+    if (w->post_norm_w) {
+        if (!(dims->rms_eps > 0.0f)) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp: invalid shape or epsilon");
+        const int st = gemma_rms_norm(ws, residual, w->post_norm_w, dims->hidden_size, tokens,
+                                      dims->rms_eps, dims->norm_style == 0, (cudaStream_t)stream);
+        if (st) return st;
+        normed = ws;
+    }
+    return mlp_common((cudaStream_t)stream, normed, ws, layer_out, w, tokens, dims);
+}
+
+int ffn_forward_mlp_prepared(void *cublas, void *stream, const void *normed, void *ws, void *layer_out,
+                             const FfnMlpWeights *w, int tokens, const FfnModelDims *dims) {
+    (void)cublas;
+    clear_error();
+    const int c = check_mlp("ffn_forward_mlp_prepared", normed, ws, layer_out, w, tokens, dims);
+    if (c) return c;
+    return mlp_common((cudaStream_t)stream, normed, ws, layer_out, w, tokens, dims);
+}
+
+/* ---- the reference's kernel test bridge ---------------------------------------------------- */
+
+int test_gemm_int4(void *out, const void *a, const void *packed, const void *scales, int M, int N,
+                   int K, int group) {
+    clear_error();
+    const int c = check_gemm("test_gemm_int4", a ? a : (const void *)16, packed ? packed : (const void *)16,
+                             scales, out, M, N, K, group);
+    if (c == 1) return 0;
+    if (c) { fprintf(stderr, "test_gemm_int4: %s\n", g_error); return -1; }
+    if (!a || !packed) { fprintf(stderr, "test_gemm_int4: null buffer\n"); return -1; }
+    Staged so, sa, sp, ss;
+    int st = so.acquire(out, (size_t)M * N * 2, true);
+    if (!st) st = sa.acquire(a, (size_t)M * K * 2, false);
+    if (!st) st = sp.acquire(packed, (size_t)N * K / 2, false);
+    if (!st) st = ss.acquire(scales, (size_t)N * (K / group) * 2, false);
+    if (!st) st = gemm_int4_dispatch(sa.dev, sp.dev, ss.dev, so.dev, M, N, K, nullptr);
+    if (st) { fprintf(stderr, "test_gemm_int4: %s\n", g_error); return -1; }
+    const cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e;
+    return so.finish() ? -1 : 0;
+}
+
+int test_silu_mul_packed(void *out, const void *packed, int tokens, int intermediate) {
+    clear_error();
+    if (tokens < 0 || intermediate < 0) { fprintf(stderr, "test_silu_mul_packed: negative extent\n"); return -1; }
+    if (tokens == 0 || intermediate == 0) return 0;
+    if (!out || !packed) { fprintf(stderr, "test_silu_mul_packed: null buffer\n"); return -1; }
+    Staged so, sp;
+    int st = so.acquire(out, (size_t)tokens * intermediate * 2, true);
+    if (!st) st = sp.acquire(packed, (size_t)tokens * intermediate * 4, false);
+    if (!st) st = silu_mul_packed(so.dev, sp.dev, tokens, intermediate, nullptr);
+    if (st) { fprintf(stderr, "test_silu_mul_packed: %s\n", g_error); return -1; }
+    const cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e;
+    return so.finish() ? -1 : 0;
+}
+
+int test_norm(void *out, const void *x, const void *weight, int rows, int cols) {
+    clear_error();
+    if (rows < 0 || cols <= 0) { fprintf(stderr, "test_norm: invalid shape or epsilon\n"); return -1; }
+    if (rows == 0) return 0;
+    if (!out || !x || !weight) { fprintf(stderr, "test_norm: null buffer\n"); return -1; }
+    Staged so, sx, sw;
+    int st = so.acquire(out, (size_t)rows * cols * 2, true);
+    if (!st) st = sx.acquire(x, (size_t)rows * cols * 2, false);
+    if (!st) st = sw.acquire(weight, (size_t)cols * 2, false);
+    if (!st) st = gemma_rms_norm(so.dev, sx.dev, sw.dev, cols, rows, 1e-6f, 1, nullptr);
+    if (st) { fprintf(stderr, "test_norm: %s\n", g_error); return -1; }
+    const cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e;
+    return so.finish() ? -1 : 0;
+}
+
+}  // extern "C"

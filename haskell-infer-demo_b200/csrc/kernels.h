@@ -1,0 +1,31 @@
+/* kernels.h - internal (C++) interface between the kernel translation units and the C ABI. */
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ffn_int4.h"
+
+namespace ffn {
+
+/* basic_kernels.cu */
+int gemm_int4_generic(const void *a, const void *packed, const void *scales, void *out_bf16,
+                      float *out_f32, int M, int N, int K, cudaStream_t stream);
+int silu_mul_packed(void *out, const void *packed, int tokens, int inter, cudaStream_t stream);
+int gemma_rms_norm(void *out, const void *x, const void *w, int cols, int rows, float eps, int gemma,
+                   cudaStream_t stream);
+int residual_add(void *dst, const void *src, int n, cudaStream_t stream);
+int dequantize_int4(void *out, const void *packed, const void *scales, int N, int K, int *bad,
+                    cudaStream_t stream);
+
+/* ffn_fused.cu */
+#define FFN_NOT_ADMITTED 1 /* internal: the fused kernel does not take this shape */
+struct FusedArgsFwd;
+/* M-dispatching GEMM: decode-shaped calls go to the streaming kernels, the rest to the generic one. */
+int gemm_int4_dispatch(const void *a, const void *packed, const void *scales, void *out, int M, int N,
+                       int K, cudaStream_t stream);
+/* The single-launch fused FFN (gate/up + SiLU*up + down).  Returns FFN_NOT_ADMITTED when the shape
+ * is outside what it supports, so the caller can take the three-kernel route. */
+int fused_ffn_try(cudaStream_t stream, const void *normed, void *act, void *layer_out,
+                  const FfnMlpWeights *w, int tokens, int H, int I);
+
+}  // namespace ffn

@@ -1,0 +1,85 @@
+"""ctypes binding of libffn_int4.so.  Fails loudly when the library is absent."""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libffn_int4.so")
+HEADER = os.path.join(HERE, "..", "include", "ffn_int4.h")
+_lib = None
+
+
+class LibraryMissing(RuntimeError):
+    pass
+
+
+class FfnError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"libffn_int4 status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+class MlpWeights(ctypes.Structure):
+    """Mirror of FfnMlpWeights (= the reference's MlpWeights, csrc/include/layers.h:54-70)."""
+    _fields_ = [("gate_proj_w", ctypes.c_void_p), ("up_proj_w", ctypes.c_void_p),
+                ("down_proj_w", ctypes.c_void_p), ("post_norm_w", ctypes.c_void_p),
+                ("gate_up_i4", ctypes.c_void_p), ("gate_up_i4_scales", ctypes.c_void_p),
+                ("down_i4", ctypes.c_void_p), ("down_i4_scales", ctypes.c_void_p),
+                ("i4_group", ctypes.c_int)]
+
+
+class ModelDims(ctypes.Structure):
+    """Mirror of FfnModelDims (= the reference's ModelDims, csrc/include/layers.h:19-47)."""
+    _fields_ = [(n, ctypes.c_int) for n in (
+        "hidden_size", "intermediate_size", "num_heads", "num_kv_heads", "head_dim", "rotary_dim",
+        "norm_style", "attn_output_gate", "q_gate_interleave", "num_layers", "vocab_size")] + \
+        [("rms_eps", ctypes.c_float), ("rope_theta", ctypes.c_float)] + \
+        [(n, ctypes.c_int) for n in (
+            "max_seq_len", "gdn_conv_dim", "gdn_value_dim", "gdn_num_v_heads", "gdn_num_k_heads",
+            "gdn_head_dim", "gdn_conv_kernel", "mla_kv_lora_rank", "mla_qk_nope_head_dim",
+            "mla_qk_rope_head_dim", "mla_v_head_dim", "max_chunk")]
+
+
+def _declare(lib):
+    vp, ci, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    lib.ffn_int4_last_error.restype = ctypes.c_char_p
+    lib.ffn_int4_last_error.argtypes = []
+    sigs = {
+        "ffn_int4_abi_version": [],
+        "ffn_gemm_int4_bf16": [vp, vp, vp, vp, ci, ci, ci, ci, vp],
+        "ffn_silu_mul_packed": [vp, vp, ci, ci, vp],
+        "ffn_gemma_rms_norm": [vp, vp, vp, ci, ci, cf, vp],
+        "ffn_residual_add": [vp, vp, ci, vp],
+        "ffn_dequantize_int4": [vp, vp, vp, ci, ci, vp, vp],
+        "ffn_forward_mlp": [vp, vp, vp, vp, vp, ctypes.POINTER(MlpWeights), ci, ctypes.POINTER(ModelDims)],
+        "ffn_forward_mlp_prepared": [vp, vp, vp, vp, vp, ctypes.POINTER(MlpWeights), ci,
+                                     ctypes.POINTER(ModelDims)],
+        "test_gemm_int4": [vp, vp, vp, vp, ci, ci, ci, ci],
+        "test_silu_mul_packed": [vp, vp, ci, ci],
+        "test_norm": [vp, vp, vp, ci, ci],
+    }
+    for name, args in sigs.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = ci
+    return lib
+
+
+def load():
+    """The loaded library.  Raises LibraryMissing if it was never built (run
+    ``python haskell-infer-demo_b200/build.py``); there is no fallback implementation."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise LibraryMissing(
+                f"{LIB_PATH} is missing: build it with `python haskell-infer-demo_b200/build.py`; "
+                "this package has no CPU or PyTorch fallback")
+        _lib = _declare(ctypes.CDLL(LIB_PATH))
+    return _lib
+
+
+def check(status):
+    """Raise FfnError for a negative status, carrying the library's message."""
+    if status != 0:
+        raise FfnError(status, load().ffn_int4_last_error().decode("utf-8", "replace"))
+    return status

@@ -1,0 +1,124 @@
+"""Host-side mirror of the reference's operator interface for the INT4 FFN path, over torch CUDA
+tensors.  Each function validates nothing itself: arguments go to the C ABI unchanged and the
+library's status/last-error is raised as :class:`FfnError`, so error behaviour is the library's.
+
+Names follow the reference: ``gemm_int4_bf16`` (csrc/include/layers.h:376), ``forward_mlp`` /
+``forward_mlp_prepared`` (layers.h:330-337), ``kernel_silu_mul_packed`` (kernels.h),
+``kernel_gemma_rms_norm``, ``kernel_residual_add``.
+"""
+import ctypes
+
+import torch
+
+from .lib import MlpWeights, ModelDims, check, load
+
+GROUP = 128
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("this path runs on CUDA tensors only; there is no CPU implementation")
+
+
+def gemm_int4_bf16(a, packed, scales, group=GROUP):
+    """a bf16 [M, K]; packed uint8 [N, K/2]; scales bf16-bits (int16/uint16/bfloat16) [N, K/128]
+    -> bf16 [M, N]."""
+    _require_cuda(a, packed, scales)
+    m, k = a.shape
+    n = packed.shape[0]
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    check(load().ffn_gemm_int4_bf16(_ptr(a), _ptr(packed), _ptr(scales), _ptr(out), m, n, k, group,
+                                    _stream()))
+    return out
+
+
+def kernel_silu_mul_packed(packed_act):
+    """bf16 [T, 2I] (gate half then up half per row) -> bf16 [T, I]."""
+    _require_cuda(packed_act)
+    t, two_i = packed_act.shape
+    out = torch.empty((t, two_i // 2), dtype=torch.bfloat16, device=packed_act.device)
+    check(load().ffn_silu_mul_packed(_ptr(out), _ptr(packed_act), t, two_i // 2, _stream()))
+    return out
+
+
+def kernel_gemma_rms_norm(x, weight, eps=1e-6):
+    _require_cuda(x, weight)
+    rows, cols = x.shape
+    out = torch.empty_like(x)
+    check(load().ffn_gemma_rms_norm(_ptr(out), _ptr(x), _ptr(weight), cols, rows, eps, _stream()))
+    return out
+
+
+def kernel_residual_add(dst, src):
+    _require_cuda(dst, src)
+    check(load().ffn_residual_add(_ptr(dst), _ptr(src), dst.numel(), _stream()))
+    return dst
+
+
+def dequantize_int4(packed, scales):
+    """float(code) * float(scale) through the kernels' unpack routine -> (fp32 [N, K], count of
+    reserved 0x8 nibbles)."""
+    _require_cuda(packed, scales)
+    n, kb = packed.shape
+    out = torch.empty((n, kb * 2), dtype=torch.float32, device=packed.device)
+    bad = torch.zeros(1, dtype=torch.int32, device=packed.device)
+    check(load().ffn_dequantize_int4(_ptr(out), _ptr(packed), _ptr(scales), n, kb * 2, _ptr(bad),
+                                     _stream()))
+    return out, int(bad.item())
+
+
+class DenseMlp:
+    """One layer's (rank-local) INT4 operands on the device, shaped like the reference's
+    MlpWeights: gate_up [2I, H/2] u8 + scales [2I, H/128], down [H, I/2] u8 + scales [H, I/128],
+    optional post-norm weight bf16 [H]."""
+
+    def __init__(self, gate_up, gate_up_scales, down, down_scales, post_norm_w=None, rms_eps=1e-6,
+                 max_chunk=128):
+        _require_cuda(gate_up, gate_up_scales, down, down_scales, post_norm_w)
+        self.tensors = (gate_up, gate_up_scales, down, down_scales, post_norm_w)  # keep alive
+        self.hidden = gate_up.shape[1] * 2
+        self.inter = gate_up.shape[0] // 2
+        self.weights = MlpWeights(0, 0, 0, post_norm_w.data_ptr() if post_norm_w is not None else 0,
+                                  gate_up.data_ptr(), gate_up_scales.data_ptr(), down.data_ptr(),
+                                  down_scales.data_ptr(), GROUP)
+        self.dims = ModelDims()
+        self.dims.hidden_size = self.hidden
+        self.dims.intermediate_size = self.inter
+        self.dims.norm_style = 0
+        self.dims.rms_eps = rms_eps
+        self.dims.max_chunk = max_chunk
+        self.device = gate_up.device
+
+    def workspace(self, tokens):
+        """The reference's layer workspace for the MLP: tokens*(H+3I) bf16 (layers.cu:65)."""
+        return torch.empty(tokens * (self.hidden + 3 * self.inter), dtype=torch.bfloat16,
+                           device=self.device)
+
+    def forward_mlp(self, residual, ws=None, layer_out=None):
+        """norm (when the layer has a post-norm weight) + FFN; returns layer_out bf16 [T, H]."""
+        tokens = residual.shape[0]
+        ws = self.workspace(tokens) if ws is None else ws
+        layer_out = torch.empty((tokens, self.hidden), dtype=torch.bfloat16,
+                                device=self.device) if layer_out is None else layer_out
+        check(load().ffn_forward_mlp(None, _stream(), _ptr(residual), _ptr(ws), _ptr(layer_out),
+                                     ctypes.byref(self.weights), tokens, ctypes.byref(self.dims)))
+        return layer_out
+
+    def forward_mlp_prepared(self, normed, ws=None, layer_out=None):
+        tokens = normed.shape[0]
+        ws = self.workspace(tokens) if ws is None else ws
+        layer_out = torch.empty((tokens, self.hidden), dtype=torch.bfloat16,
+                                device=self.device) if layer_out is None else layer_out
+        check(load().ffn_forward_mlp_prepared(None, _stream(), _ptr(normed), _ptr(ws), _ptr(layer_out),
+                                              ctypes.byref(self.weights), tokens,
+                                              ctypes.byref(self.dims)))
+        return layer_out

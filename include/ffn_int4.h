@@ -1,0 +1,156 @@
+/*
+ * ffn_int4.h - C ABI of libffn_int4.so: the weight-only INT4 (symmetric, group 128, BF16 scales)
+ * dense-FFN decode path for NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only.  Every entry point returns FFN_OK (0) or a negative status and
+ * leaves a message in ffn_int4_last_error() (thread-local, valid until the next call on the
+ * thread) - the convention of the reference engine ABI (csrc/include/engine.h:264-276).  No C++
+ * exception crosses this boundary.  All device pointers belong to the CUDA device that is current
+ * on the calling thread; `stream` arguments are `cudaStream_t` passed as `void *` (NULL = the
+ * default stream).  There is no CPU fallback: without a usable CUDA device every compute entry
+ * point fails with FFN_ERR_CUDA.
+ *
+ * Data layouts (identical to the reference's, csrc/include/linear_weight.h:12-13, 46-54):
+ *   packed [N][K/2]   u8, row-major; byte j of a row = code(k=2j) | code(k=2j+1) << 4; codes are
+ *                     4-bit two's complement in [-7, 7]; 0x8 is the reserved invalid code
+ *   scales [N][K/128] bf16, row-major (row, group)
+ *   gate/up pair      [2*I_local][H]: the rank's gate rows, then its up rows
+ *   down              [H][I_local]
+ *   activations       bf16 [M][H]; outputs bf16 [M][H]
+ */
+#ifndef FFN_INT4_H
+#define FFN_INT4_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FFN_INT4_ABI_VERSION 1
+#define FFN_INT4_GROUP 128
+
+/* Status codes: the values of ENGINE_OK / ENGINE_ERR_* (csrc/include/engine.h:264-270). */
+#define FFN_OK 0
+#define FFN_ERR_CUDA (-1)    /* CUDA runtime error, or a bounded device-side wait ran out */
+#define FFN_ERR_ALLOC (-2)   /* device or host allocation failed */
+#define FFN_ERR_WEIGHTS (-3) /* artifact / manifest refused */
+#define FFN_ERR_CONFIG (-4)  /* invalid argument or unsupported shape */
+#define FFN_ERR_STATE (-5)   /* call order or object state */
+
+/* Replaces engine_last_error (csrc/include/engine.h:272-276) for this library's calls. */
+const char *ffn_int4_last_error(void);
+int ffn_int4_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------- */
+/* Operator level                                                                              */
+/* ------------------------------------------------------------------------------------------- */
+
+/* Replaces gemm_int4_bf16 (csrc/include/layers.h:376-377; csrc/kernels/gemm_quant.cu:204-254).
+ * out[M][N] (bf16) = a[M][K] (bf16) x dequant(packed, scales)[N][K]^T, FP32 accumulation, one
+ * BF16 rounding.  Same refusals as the reference, returned as FFN_ERR_CONFIG instead of thrown:
+ * negative extent, K <= 0, group <= 0, null buffer, K not a whole number of groups; this
+ * library additionally requires group == 128 (the only group the format defines,
+ * csrc/linear_weight.cpp:63-68).  M == 0 or N == 0 is a successful no-op.  Asynchronous on
+ * `stream`. */
+int ffn_gemm_int4_bf16(const void *a, const void *packed, const void *scales, void *out, int M,
+                       int N, int K, int group, void *stream);
+
+/* Replaces kernel_silu_mul_packed (csrc/kernels/silu.cu:76-95): out[t][i] =
+ * bf16(silu(packed[t][i]) * packed[t][I + i]); packed is bf16 [tokens][2I]. */
+int ffn_silu_mul_packed(void *out, const void *packed, int tokens, int intermediate, void *stream);
+
+/* Replaces kernel_gemma_rms_norm (csrc/kernels/flashinfer_norm.cu:22-44): out = bf16(x *
+ * rsqrt(mean(x^2) + eps) * (1 + w)) per row, FP32 arithmetic. */
+int ffn_gemma_rms_norm(void *out, const void *x, const void *weight, int cols, int rows, float eps,
+                       void *stream);
+
+/* Replaces kernel_residual_add (csrc/kernels/gdn_norm.cu:121-136): dst = bf16(f32(dst)+f32(src)). */
+int ffn_residual_add(void *dst, const void *src, int n, void *stream);
+
+/* Writes float(code) * float(scale) for every element of a packed [N][K] weight to out (FP32
+ * [N][K]) using the same unpack routine the GEMV kernels use.  Exists so the "dequantized
+ * weights are bit-exact" bar can be checked against linear_dequantize_int4
+ * (csrc/linear_weight.cpp:178-216).  `bad` (device int, may be NULL) receives the number of
+ * reserved 0x8 nibbles met. */
+int ffn_dequantize_int4(void *out, const void *packed, const void *scales, int N, int K, int *bad,
+                        void *stream);
+
+/* Field-for-field mirror of the reference's MlpWeights (csrc/include/layers.h:54-70), so the
+ * engine's own struct can be passed unchanged.  Only the INT4 members and post_norm_w are read. */
+typedef struct {
+    const void *gate_proj_w;
+    const void *up_proj_w;
+    const void *down_proj_w;
+    const void *post_norm_w;       /* bf16 [H], raw Gemma weight; NULL skips the norm */
+    const uint8_t *gate_up_i4;     /* [2I][H/2] */
+    const void *gate_up_i4_scales; /* bf16 [2I][H/128] */
+    const uint8_t *down_i4;        /* [H][I/2] */
+    const void *down_i4_scales;    /* bf16 [H][I/128] */
+    int i4_group;
+} FfnMlpWeights;
+
+/* Field-for-field mirror of the reference's ModelDims (csrc/include/layers.h:19-47).  Read:
+ * hidden_size, intermediate_size (the rank-local one), norm_style (0 = Gemma), rms_eps,
+ * max_chunk. */
+typedef struct {
+    int hidden_size;
+    int intermediate_size;
+    int num_heads;
+    int num_kv_heads;
+    int head_dim;
+    int rotary_dim;
+    int norm_style;
+    int attn_output_gate;
+    int q_gate_interleave;
+    int num_layers;
+    int vocab_size;
+    float rms_eps;
+    float rope_theta;
+    int max_seq_len;
+    int gdn_conv_dim;
+    int gdn_value_dim;
+    int gdn_num_v_heads;
+    int gdn_num_k_heads;
+    int gdn_head_dim;
+    int gdn_conv_kernel;
+    int mla_kv_lora_rank;
+    int mla_qk_nope_head_dim;
+    int mla_qk_rope_head_dim;
+    int mla_v_head_dim;
+    int max_chunk;
+} FfnModelDims;
+
+/* Replaces forward_mlp (csrc/include/layers.h:335-337; csrc/kernels/layers.cu:149-160) for the
+ * INT4 operands: post-norm (when post_norm_w is set) -> gate/up -> SiLU*up -> down, written to
+ * layer_out [tokens][H] as BF16 with the reference's three rounding points.  `cublas` is
+ * accepted and ignored (no cuBLAS on this path).  `ws` is the reference's workspace
+ * (tokens*(H+3I) bf16, csrc/kernels/layers.cu:65, 117-118); the normalized activation is left
+ * in ws[0 .. tokens*H) as the reference leaves it, and the activation a in its usual slot.  Unlike the reference
+ * (csrc/kernels/layers.cu:126) every token count in [1, max_chunk] takes the INT4 path; a
+ * weight set without INT4 operands is refused with FFN_ERR_CONFIG (there is no BF16 path here). */
+int ffn_forward_mlp(void *cublas, void *stream, const void *residual, void *ws, void *layer_out,
+                    const FfnMlpWeights *w, int tokens, const FfnModelDims *dims);
+
+/* Replaces forward_mlp_prepared (csrc/include/layers.h:330-333): as above from an already
+ * normalized activation. */
+int ffn_forward_mlp_prepared(void *cublas, void *stream, const void *normed, void *ws,
+                             void *layer_out, const FfnMlpWeights *w, int tokens,
+                             const FfnModelDims *dims);
+
+/* ------------------------------------------------------------------------------------------- */
+/* The reference's kernel test bridge (tests/kernels/kernel_bridge.cu), same names and           */
+/* signatures, so the reference's own gate scripts can be pointed at this library.  Synchronous. */
+/* Every pointer may be a host pointer or a device pointer; host buffers are staged.            */
+/* ------------------------------------------------------------------------------------------- */
+int test_gemm_int4(void *out, const void *a, const void *packed, const void *scales, int M, int N,
+                   int K, int group);                                     /* kernel_bridge.cu:83-95 */
+int test_silu_mul_packed(void *out, const void *packed, int tokens, int intermediate); /* :68-79 */
+int test_norm(void *out, const void *x, const void *weight, int rows, int cols);       /* :31-41 */
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FFN_INT4_H */

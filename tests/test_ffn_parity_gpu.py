@@ -1,0 +1,65 @@
+"""GPU parity of the FFN operator (ffn_forward_mlp through the C ABI) against the CPU oracle on the
+seeded configurations, plus the committed golden output of config 0."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ffn_oracle as o
+from gpu_util import assert_ffn_close, dev_bf16, host_f32, upload_layer
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+@pytest.mark.parametrize("cfg,tokens", [(0, 1), (0, 2), (0, 4), (0, 8), (1, 1), (2, 1)])
+def test_ffn_matches_oracle(cuda, cfg, tokens):
+    spec = o.CONFIGS[cfg]
+    x, layers = o.draw_config(spec["hidden"], spec["inter"], spec["seed"], tokens=tokens)
+    want = o.ffn(layers[0], x)
+    mlp = upload_layer(layers[0], cuda)
+    got = host_f32(mlp.forward_mlp_prepared(dev_bf16(x, cuda)))
+    torch.cuda.synchronize()
+    max_abs, rel = assert_ffn_close(got, want, f"config {cfg} M={tokens}")
+    print(f"config {cfg} M={tokens}: max-abs {max_abs:.3g} rel-L2 {rel:.3g}")
+
+
+def test_config0_golden_output(cuda):
+    """Against the committed fixture (made from weights the reference library quantized)."""
+    with open(os.path.join(GOLDEN, "ffn_config0.json")) as f:
+        fx = json.load(f)
+    x, layers = o.draw_config(fx["hidden"], fx["inter"], fx["seed"])
+    want = o.bf16_to_f32(np.array(fx["y_bf16"], np.uint16)).reshape(1, -1)
+    mlp = upload_layer(layers[0], cuda)
+    got = host_f32(mlp.forward_mlp_prepared(dev_bf16(x, cuda)))
+    assert_ffn_close(got, want, "config 0 golden")
+
+
+def test_forward_mlp_with_norm_and_workspace_layout(cuda):
+    """forward_mlp applies the Gemma post-norm first and leaves the normalized activation at the
+    start of the workspace, as the reference does (csrc/kernels/layers.cu:149-160)."""
+    x, layers = o.draw_config(1024, 3072, 7, tokens=2, with_norm=True)
+    lay = layers[0]
+    normed = o.gemma_rmsnorm(x, lay.w_norm)
+    want = o.ffn(lay, normed)
+    mlp = upload_layer(lay, cuda, with_norm=True)
+    ws = mlp.workspace(2)
+    got = host_f32(mlp.forward_mlp(dev_bf16(x, cuda), ws=ws))
+    torch.cuda.synchronize()
+    ws_normed = host_f32(ws[:2 * 1024].view(2, 1024))
+    assert np.allclose(ws_normed, normed, atol=1e-3, rtol=8e-3)
+    assert_ffn_close(got, o.ffn(lay, ws_normed), "forward_mlp vs oracle on the device's own norm")
+    assert o.compare(got, want)[1] <= 5e-3
+
+
+def test_refusals(cuda):
+    from haskell_infer_demo_b200.lib import FfnError
+    x, layers = o.draw_config(256, 512, 1)
+    mlp = upload_layer(layers[0], cuda)
+    with pytest.raises(FfnError, match="max_chunk"):
+        mlp.forward_mlp_prepared(torch.zeros((129, 256), dtype=torch.bfloat16, device=cuda))
+    mlp.weights.gate_up_i4 = 0
+    with pytest.raises(FfnError, match="no INT4 operands"):
+        mlp.forward_mlp_prepared(dev_bf16(x, cuda))
