@@ -16,6 +16,7 @@
 namespace ffn {
 
 static thread_local char g_error[512];
+static int g_fused_enabled = 1;
 
 int fail(int status, const char *fmt, ...) {
     va_list ap;
@@ -50,7 +51,7 @@ static int mlp_common(cudaStream_t stream, const void *normed, void *ws, void *l
     uint16_t *base = (uint16_t *)ws;
     uint16_t *packed_act = base + (size_t)tokens * H;            /* [T, 2I] gate|up */
     uint16_t *act = packed_act + (size_t)2 * tokens * I;         /* [T, I] */
-    int st = fused_ffn_try(stream, normed, act, layer_out, w, tokens, H, I);
+    int st = g_fused_enabled ? fused_ffn_try(stream, normed, act, layer_out, w, tokens, H, I) : FFN_NOT_ADMITTED;
     if (st != FFN_NOT_ADMITTED) return st;
     st = gemm_int4_generic(normed, w->gate_up_i4, w->gate_up_i4_scales, packed_act, nullptr, tokens,
                            2 * I, H, stream);
@@ -117,6 +118,32 @@ extern "C" {
 
 const char *ffn_int4_last_error(void) { return g_error; }
 int ffn_int4_abi_version(void) { return FFN_INT4_ABI_VERSION; }
+
+int ffn_int4_set_fused(int enabled) {
+    const int old = g_fused_enabled;
+    g_fused_enabled = enabled != 0;
+    return old;
+}
+
+int ffn_int4_device_status(int *where, int *cta) {
+    clear_error();
+    unsigned st = 0;
+    const cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(FFN_ERR_CUDA, "ffn_int4_device_status: %s", cudaGetErrorString(e));
+    const int rc = fused_status(&st, true);
+    if (rc) return rc;
+    if (where) *where = (int)(st & 0xFF);
+    if (cta) *cta = (int)(st >> 8);
+    if (st != 0) {
+        static const char *names[] = {"", "producer waiting for a free stage", "consumer waiting for weights",
+                                      "consumer waiting for a partial slot", "epilogue waiting for partials",
+                                      "grid barrier", "peer arrival flag", "draining copies"};
+        const unsigned w = st & 0xFF;
+        return fail(FFN_ERR_CUDA, "a bounded device-side wait ran out (%s, CTA %u); the kernel returned early and "
+                    "its output is invalid", w < 8 ? names[w] : "unknown", st >> 8);
+    }
+    return FFN_OK;
+}
 
 int ffn_gemm_int4_bf16(const void *a, const void *packed, const void *scales, void *out, int M, int N,
                        int K, int group, void *stream) {

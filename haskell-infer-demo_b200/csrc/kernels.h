@@ -19,7 +19,6 @@ int dequantize_int4(void *out, const void *packed, const void *scales, int N, in
 
 /* ffn_fused.cu */
 #define FFN_NOT_ADMITTED 1 /* internal: the fused kernel does not take this shape */
-struct FusedArgsFwd;
 /* M-dispatching GEMM: decode-shaped calls go to the streaming kernels, the rest to the generic one. */
 int gemm_int4_dispatch(const void *a, const void *packed, const void *scales, void *out, int M, int N,
                        int K, cudaStream_t stream);
@@ -27,5 +26,20 @@ int gemm_int4_dispatch(const void *a, const void *packed, const void *scales, vo
  * is outside what it supports, so the caller can take the three-kernel route. */
 int fused_ffn_try(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                   const FfnMlpWeights *w, int tokens, int H, int I);
+
+/* Tensor-parallel exchange tables (device arrays of per-rank pointers, set up once at load). */
+struct FusedTp {
+    int tp, rank;
+    float *const *peer_slots;    /* [tp] -> each rank's [2][tp][slot_stride] fp32 */
+    unsigned *const *peer_flags; /* [tp] -> each rank's per-CTA arrival counters */
+    int slot_stride;             /* floats per (parity, rank) slot */
+    int max_ctas;                /* grid size every rank uses */
+};
+int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
+                     const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual);
+/* Reads (synchronously) the status word the fused kernel writes when a bounded wait runs out:
+ * 0 = fine, else (where | cta << 8).  With reset, a non-zero status also clears the kernel's
+ * synchronisation words so the next launch starts clean. */
+int fused_status(unsigned *status_out, bool reset);
 
 }  // namespace ffn

@@ -46,6 +46,8 @@ def _declare(lib):
     lib.ffn_int4_last_error.argtypes = []
     sigs = {
         "ffn_int4_abi_version": [],
+        "ffn_int4_device_status": [ctypes.POINTER(ci), ctypes.POINTER(ci)],
+        "ffn_int4_set_fused": [ci],
         "ffn_gemm_int4_bf16": [vp, vp, vp, vp, ci, ci, ci, ci, vp],
         "ffn_silu_mul_packed": [vp, vp, ci, ci, vp],
         "ffn_gemma_rms_norm": [vp, vp, vp, ci, ci, cf, vp],
@@ -76,6 +78,12 @@ def load():
                 "this package has no CPU or PyTorch fallback")
         _lib = _declare(ctypes.CDLL(LIB_PATH))
     return _lib
+
+
+def device_status():
+    """Synchronise and raise FfnError if a fused kernel gave up on a bounded wait."""
+    where, cta = ctypes.c_int(0), ctypes.c_int(0)
+    return check(load().ffn_int4_device_status(ctypes.byref(where), ctypes.byref(cta)))
 
 
 def check(status):

@@ -43,6 +43,20 @@ extern "C" {
 const char *ffn_int4_last_error(void);
 int ffn_int4_abi_version(void);
 
+/* Synchronises the current device and reports whether any fused kernel since the last call gave
+ * up on a bounded wait (every device-side wait in this library has an iteration limit; on expiry
+ * the kernel records where and returns instead of hanging).  Returns FFN_OK, or FFN_ERR_CUDA with
+ * `where` (1..7) and `cta` filled; a non-zero status is cleared and the kernel's synchronisation
+ * words are reset, the analogue of the reference's "failed forward needs engine_reset"
+ * (csrc/engine.cu:1723-1730).  No counterpart function in the reference. */
+int ffn_int4_device_status(int *where, int *cta);
+
+/* Chooses between the single-launch fused FFN kernel (default, 1) and the three-kernel route
+ * (gate/up GEMM, SiLU*up, down GEMM - the reference's launch structure, csrc/kernels/layers.cu:
+ * 127-145) for ffn_forward_mlp*.  Both are CUDA paths; the switch exists for A/B measurement.
+ * Returns the previous setting. */
+int ffn_int4_set_fused(int enabled);
+
 /* ------------------------------------------------------------------------------------------- */
 /* Operator level                                                                              */
 /* ------------------------------------------------------------------------------------------- */

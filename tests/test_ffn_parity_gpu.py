@@ -7,6 +7,7 @@ import numpy as np
 import pytest
 import torch
 
+from haskell_infer_demo_b200 import lib as L
 from oracle import ffn_oracle as o
 from gpu_util import assert_ffn_close, dev_bf16, host_f32, upload_layer
 
@@ -14,16 +15,51 @@ pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
-@pytest.mark.parametrize("cfg,tokens", [(0, 1), (0, 2), (0, 4), (0, 8), (1, 1), (2, 1)])
-def test_ffn_matches_oracle(cuda, cfg, tokens):
-    spec = o.CONFIGS[cfg]
-    x, layers = o.draw_config(spec["hidden"], spec["inter"], spec["seed"], tokens=tokens)
-    want = o.ffn(layers[0], x)
-    mlp = upload_layer(layers[0], cuda)
-    got = host_f32(mlp.forward_mlp_prepared(dev_bf16(x, cuda)))
-    torch.cuda.synchronize()
-    max_abs, rel = assert_ffn_close(got, want, f"config {cfg} M={tokens}")
-    print(f"config {cfg} M={tokens}: max-abs {max_abs:.3g} rel-L2 {rel:.3g}")
+@pytest.fixture(scope="module")
+def drawn():
+    cache = {}
+
+    def get(cfg, tokens):
+        if (cfg, tokens) not in cache:
+            spec = o.CONFIGS[cfg]
+            x, layers = o.draw_config(spec["hidden"], spec["inter"], spec["seed"], tokens=tokens)
+            cache[(cfg, tokens)] = (x, layers[0], o.ffn(layers[0], x))
+        return cache[(cfg, tokens)]
+    return get
+
+
+@pytest.mark.parametrize("fused", [1, 0])
+@pytest.mark.parametrize("cfg,tokens", [(0, 1), (0, 2), (0, 4), (0, 8), (1, 1), (1, 2), (2, 1), (2, 2)])
+def test_ffn_matches_oracle(cuda, drawn, cfg, tokens, fused):
+    """Single-launch fused kernel (M <= 2) and the three-kernel route against the CPU oracle."""
+    x, layer, want = drawn(cfg, tokens)
+    mlp = upload_layer(layer, cuda)
+    old = L.load().ffn_int4_set_fused(fused)
+    try:
+        got = host_f32(mlp.forward_mlp_prepared(dev_bf16(x, cuda)))
+        L.device_status()
+    finally:
+        L.load().ffn_int4_set_fused(old)
+    max_abs, rel = assert_ffn_close(got, want, f"config {cfg} M={tokens} fused={fused}")
+    print(f"config {cfg} M={tokens} fused={fused}: max-abs {max_abs:.3g} rel-L2 {rel:.3g}")
+
+
+def test_fused_is_deterministic_and_repeatable(cuda, drawn):
+    """Same inputs, many launches: bit-identical outputs (fixed-order reductions, self-resetting
+    grid barrier) and the activation left in the workspace equals the oracle's within one ulp."""
+    x, layer, want = drawn(1, 1)
+    mlp = upload_layer(layer, cuda)
+    xd = dev_bf16(x, cuda)
+    ws = mlp.workspace(1)
+    first = mlp.forward_mlp_prepared(xd, ws=ws).clone()
+    for _ in range(20):
+        again = mlp.forward_mlp_prepared(xd, ws=ws)
+        assert torch.equal(first.view(torch.int16), again.view(torch.int16))
+    L.device_status()
+    _, gu, act = o.ffn(layer, x, intermediates=True)
+    h, i = layer.hidden, layer.inter
+    got_act = host_f32(ws[h + 2 * i:h + 3 * i].view(1, i))
+    assert o.compare(got_act, act)[1] <= 5e-3
 
 
 def test_config0_golden_output(cuda):
@@ -34,6 +70,7 @@ def test_config0_golden_output(cuda):
     want = o.bf16_to_f32(np.array(fx["y_bf16"], np.uint16)).reshape(1, -1)
     mlp = upload_layer(layers[0], cuda)
     got = host_f32(mlp.forward_mlp_prepared(dev_bf16(x, cuda)))
+    L.device_status()
     assert_ffn_close(got, want, "config 0 golden")
 
 
