@@ -125,6 +125,8 @@ int ffn_int4_set_fused(int enabled) {
     return old;
 }
 
+void ffn_int4_debug_trace(void *device_buffer) { fused_set_trace((long long *)device_buffer); }
+
 int ffn_int4_device_status(int *where, int *cta) {
     clear_error();
     unsigned st = 0;
@@ -137,10 +139,11 @@ int ffn_int4_device_status(int *where, int *cta) {
     if (st != 0) {
         static const char *names[] = {"", "producer waiting for a free stage", "consumer waiting for weights",
                                       "consumer waiting for a partial slot", "epilogue waiting for partials",
-                                      "grid barrier", "peer arrival flag", "draining copies"};
+                                      "grid barrier", "peer arrival flag", "draining copies",
+                                      "consumer waiting for the activation vector"};
         const unsigned w = st & 0xFF;
         return fail(FFN_ERR_CUDA, "a bounded device-side wait ran out (%s, CTA %u); the kernel returned early and "
-                    "its output is invalid", w < 8 ? names[w] : "unknown", st >> 8);
+                    "its output is invalid", w < 9 ? names[w] : "unknown", st >> 8);
     }
     return FFN_OK;
 }

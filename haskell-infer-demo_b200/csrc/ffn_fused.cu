@@ -12,11 +12,15 @@
  *   warp 0        producer: streams this CTA's contiguous share of the packed weight rows from HBM
  *                 into a shared-memory ring with cp.async.bulk, completion counted on mbarriers.
  *                 The stream does not stop at the phase boundary: down-projection rows are already
- *                 in flight while the grid waits for the activation vector.
+ *                 in flight while the grid waits for the activation vector.  It also brings the
+ *                 activation vector of each phase into shared memory (x at entry, act as soon as
+ *                 the grid barrier opens).
  *   warps 1..17   consumers: thread (ct, rg) owns 16-byte column chunk(s) ct of every row r with
- *                 r % RG == rg of a tile.  Its slice of the activation vector lives in registers
- *                 for the whole phase; weights are unpacked from shared memory and multiplied with
- *                 BF16 x FP32-accumulate FMAs; half-warp shuffles reduce the row partials.
+ *                 r % RG == rg of a tile.  Its 32-element slice of the activation vector lives in
+ *                 registers for the whole phase, as 16-bit block-fixed-point split into byte planes;
+ *                 the 4-bit codes are widened to bytes with one logic op per four codes and
+ *                 multiplied with dp4a (exact integer arithmetic inside a 32-code chunk), then
+ *                 scaled once per chunk in FP32.  Half-warp shuffles reduce the row partials.
  *   warp 18       epilogue: adds the half-warp partials in a fixed order (deterministic), applies
  *                 the reference's rounding points, stores act / y, runs the grid barrier arrival and
  *                 the cross-GPU exchange.
@@ -30,6 +34,8 @@
  * Every device-side wait is bounded; on expiry the kernel records where it gave up in the status
  * word, drains its own copies and returns.  The host maps that to FFN_ERR_CUDA.
  */
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -39,17 +45,17 @@ namespace ffn {
 
 constexpr int kConsumerWarps = 17;
 constexpr int kConsumerThreads = kConsumerWarps * 32;  /* 544 = 17 * 32: I = 17408 = 17 * 1024 */
-constexpr int kEpilogueWarp = kConsumerWarps + 1;
 constexpr int kThreads = (kConsumerWarps + 2) * 32;    /* 608 */
 constexpr int kMaxStages = 8;
 constexpr int kPartSlots = 4;
 constexpr int kPartFloats = 512;                       /* floats per partial slot */
 constexpr int kMaxJT = 4;                              /* row steps per thread per tile */
 constexpr uint32_t kSpinLimit = 1u << 24;              /* bounded waits: ~1 s worst case */
+constexpr int kTraceWords = 16;
 
 /* status word values (where a wait gave up) */
 enum { ST_OK = 0, ST_PRODUCER_EMPTY = 1, ST_CONSUMER_FULL = 2, ST_PART_EMPTY = 3, ST_PART_FULL = 4,
-       ST_GRID_BARRIER = 5, ST_PEER_FLAG = 6, ST_DRAIN = 7 };
+       ST_GRID_BARRIER = 5, ST_PEER_FLAG = 6, ST_DRAIN = 7, ST_X_FULL = 8 };
 
 struct PhasePlan {
     const uint8_t *w;     /* packed rows */
@@ -67,7 +73,9 @@ struct FusedParams {
     uint16_t *out;        /* [M][H] bf16 */
     PhasePlan p1, p2;
     int M, H, I;
-    int stage_bytes, nstages;
+    int stage_bytes, nstages, xs_bytes;
+    int stage_w_bytes;    /* weights part of a stage; the tile's scales follow it */
+    int sc_half_bytes;    /* room for one contiguous run of scales (gate or up) incl. 16 bytes of slack */
     unsigned *sync;       /* [0] arrival count, [1] generation, [2] call sequence, [3] status */
     /* tensor parallelism (tp == 1: unused) */
     int tp, rank;
@@ -76,6 +84,7 @@ struct FusedParams {
     int slot_stride;      /* floats per (parity, rank) slot = M_max * H */
     /* optional fused residual update on the reduced output (h <- bf16(h + y)); NULL = off */
     uint16_t *residual;
+    long long *trace;     /* optional [kTraceWords] clock64 stamps of CTA 0 (NULL = off) */
 };
 
 /* ---- PTX wrappers -------------------------------------------------------------------------- */
@@ -92,6 +101,12 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) { /* never suspends */
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
@@ -112,11 +127,6 @@ __device__ __forceinline__ uint4 lds16(const void *p) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_u32(p)));
     return v;
 }
-__device__ __forceinline__ uint4 ldg_cg16(const void *p) { /* coherent at L2: data other CTAs just wrote */
-    uint4 v;
-    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
 __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned *p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -135,80 +145,102 @@ __device__ __forceinline__ float ld_relaxed_sys_f32(const float *p) {
     asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void named_bar_sync(int id, int threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
-/* ---- the inner product of one 16-byte chunk (32 codes) with 32 BF16 activations ------------- */
-/* (w & 0x000F000F) ^ 0x43084308 puts, in each 16-bit half, the BF16 value 128 + (code + 8): the
- * nibble XOR 8 is code+8 in [1,15] and sits in the low mantissa bits of 128.0 (0x4300).  The
- * mixed-precision FMA multiplies that BF16 by the BF16 activation exactly and accumulates in FP32,
- * so one logic op converts two codes and no integer-to-float conversion is issued.  The constant
- * 136 * sum(x) is removed once per chunk (xoff): sum((136 + c_k) x_k) - 136 sum(x_k) = sum(c_k x_k). */
 __device__ __forceinline__ uint32_t lop3_and_xor(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
     asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); /* (a & b) ^ c */
     return d;
 }
-__device__ __forceinline__ float fma_bf16_lo_lo(uint32_t a, uint32_t b, float c) {
-    float d;
-    asm("{\n.reg .b16 al, ah, bl, bh;\nmov.b32 {al, ah}, %1;\nmov.b32 {bl, bh}, %2;\nfma.rn.f32.bf16 %0, al, bl, %3;\n}"
-        : "=f"(d) : "r"(a), "r"(b), "f"(c));
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) { /* unsigned bytes x signed bytes */
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-__device__ __forceinline__ float fma_bf16_lo_hi(uint32_t a, uint32_t b, float c) {
-    float d;
-    asm("{\n.reg .b16 al, ah, bl, bh;\nmov.b32 {al, ah}, %1;\nmov.b32 {bl, bh}, %2;\nfma.rn.f32.bf16 %0, al, bh, %3;\n}"
-        : "=f"(d) : "r"(a), "r"(b), "f"(c));
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) { /* unsigned x unsigned */
+    int d;
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-__device__ __forceinline__ float fma_bf16_hi_lo(uint32_t a, uint32_t b, float c) {
-    float d;
-    asm("{\n.reg .b16 al, ah, bl, bh;\nmov.b32 {al, ah}, %1;\nmov.b32 {bl, bh}, %2;\nfma.rn.f32.bf16 %0, ah, bl, %3;\n}"
-        : "=f"(d) : "r"(a), "r"(b), "f"(c));
-    return d;
-}
-__device__ __forceinline__ float fma_bf16_hi_hi(uint32_t a, uint32_t b, float c) {
-    float d;
-    asm("{\n.reg .b16 al, ah, bl, bh;\nmov.b32 {al, ah}, %1;\nmov.b32 {bl, bh}, %2;\nfma.rn.f32.bf16 %0, ah, bh, %3;\n}"
-        : "=f"(d) : "r"(a), "r"(b), "f"(c));
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
 
-/* One 32-bit word (codes k = 8j .. 8j+7) against x pairs xr[0..3] = {x0,x1},{x2,x3},{x4,x5},{x6,x7}.
- * MT tokens share the converted weights. */
-template <int MT>
-__device__ __forceinline__ void word_dot(uint32_t w, const uint32_t (*xr)[16], int j, float (&acc)[MT]) {
-    const uint32_t v0 = lop3_and_xor(w, 0x000F000Fu, 0x43084308u);       /* k = 0 (lo), 4 (hi) */
-    const uint32_t v1 = lop3_and_xor(w >> 4, 0x000F000Fu, 0x43084308u);  /* k = 1, 5 */
-    const uint32_t v2 = lop3_and_xor(w >> 8, 0x000F000Fu, 0x43084308u);  /* k = 2, 6 */
-    const uint32_t v3 = lop3_and_xor(w >> 12, 0x000F000Fu, 0x43084308u); /* k = 3, 7 */
+/* ---- activations as block fixed point ------------------------------------------------------- */
+/* One thread's 32-element slice of an activation vector, prepared once per phase:
+ *   X_k = rint(x_k * 2^(14-E)),  E = exponent of the largest |x_k| of the slice, so |X_k| < 2^15.
+ * A BF16 value has 8 significant bits, so every element within 2^-7 of the slice maximum is held
+ * exactly; smaller ones lose only bits below max*2^-15.  X is stored as byte planes laid out for
+ * dp4a against the widened weight bytes: word j (codes k = 8j..8j+7) pairs
+ *   even codes k = 8j + {0,2,4,6}  with  he[j] (high bytes, signed) and le[j] (low bytes, unsigned)
+ *   odd  codes k = 8j + {1,3,5,7}  with  ho[j] / lo[j].
+ * xoff = 8 * sum(X) removes the +8 offset the widened codes carry; fac = 2^(E-14) undoes the scaling. */
+struct XChunk {
+    uint32_t he[4], ho[4], le[4], lo[4];
+    int xoff;
+    float fac;
+};
+
+__device__ __forceinline__ void prepare_chunk(XChunk &xc, const uint16_t *src /* shared, 64-byte aligned */, bool on) {
+    uint32_t v[16];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        const uint32_t *x = xr[m] + 4 * j;
-        float a = acc[m];
-        a = fma_bf16_lo_lo(v0, x[0], a);
-        a = fma_bf16_lo_hi(v1, x[0], a);
-        a = fma_bf16_lo_lo(v2, x[1], a);
-        a = fma_bf16_lo_hi(v3, x[1], a);
-        a = fma_bf16_hi_lo(v0, x[2], a);
-        a = fma_bf16_hi_hi(v1, x[2], a);
-        a = fma_bf16_hi_lo(v2, x[3], a);
-        a = fma_bf16_hi_hi(v3, x[3], a);
-        acc[m] = a;
+    for (int q = 0; q < 4; ++q) {
+        uint4 t = make_uint4(0, 0, 0, 0);
+        if (on) t = lds16(src + q * 8);
+        v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
     }
+    uint32_t mx = 0; /* per-halfword maximum of the magnitude bits */
+#pragma unroll
+    for (int i = 0; i < 16; ++i) mx = __vmaxu2(mx, v[i] & 0x7FFF7FFFu);
+    const uint32_t top = max(mx & 0xFFFFu, mx >> 16);
+    const int E = (int)(top >> 7); /* biased exponent of the largest magnitude */
+    /* E < 15 (|x| < 2^-112) is treated as an all-zero slice; Inf/NaN inputs are outside the contract */
+    const bool live = E >= 15 && E < 255;
+    const float up = live ? __uint_as_float((uint32_t)(268 - E) << 23) : 0.0f;   /* 2^(141-E) */
+    xc.fac = live ? __uint_as_float((uint32_t)(E - 14) << 23) : 0.0f;            /* 2^(E-141) */
+    int total_hi = 0, total_lo = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        int X[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            X[2 * i] = __float2int_rn(bf16_lo(v[4 * j + i]) * up);
+            X[2 * i + 1] = __float2int_rn(bf16_hi(v[4 * j + i]) * up);
+        }
+        /* bytes 0/1 of each X are its low/high byte (two's complement 16-bit) */
+        const uint32_t e02 = prmt(X[0], X[2], 0x5140), e46 = prmt(X[4], X[6], 0x5140); /* lo0 lo2 hi0 hi2 */
+        const uint32_t o13 = prmt(X[1], X[3], 0x5140), o57 = prmt(X[5], X[7], 0x5140);
+        xc.le[j] = prmt(e02, e46, 0x5410);
+        xc.he[j] = prmt(e02, e46, 0x7632);
+        xc.lo[j] = prmt(o13, o57, 0x5410);
+        xc.ho[j] = prmt(o13, o57, 0x7632);
+        total_hi = dp4a_us(0x01010101u, xc.he[j], total_hi);
+        total_hi = dp4a_us(0x01010101u, xc.ho[j], total_hi);
+        total_lo = dp4a_uu(0x01010101u, xc.le[j], total_lo);
+        total_lo = dp4a_uu(0x01010101u, xc.lo[j], total_lo);
+    }
+    xc.xoff = 8 * (total_hi * 256 + total_lo);
 }
 
-template <int MT>
-__device__ __forceinline__ void chunk_dot(const uint4 &w, const uint32_t (*xr)[16], float (&acc)[MT]) {
-    word_dot<MT>(w.x, xr, 0, acc);
-    word_dot<MT>(w.y, xr, 1, acc);
-    word_dot<MT>(w.z, xr, 2, acc);
-    word_dot<MT>(w.w, xr, 3, acc);
+/* sum_k code_k * X_k over one 16-byte chunk, exact. (w & 0x0F0F0F0F) ^ 0x08080808 widens the even
+ * nibbles of a word to bytes holding code+8 in [1,15]; the shifted word gives the odd nibbles. */
+__device__ __forceinline__ int chunk_dot(const uint4 &w, const XChunk &xc) {
+    int hi = 0, lo = 0;
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t e = lop3_and_xor(ws[j], 0x0F0F0F0Fu, 0x08080808u);
+        const uint32_t o = lop3_and_xor(ws[j] >> 4, 0x0F0F0F0Fu, 0x08080808u);
+        hi = dp4a_us(e, xc.he[j], hi);
+        hi = dp4a_us(o, xc.ho[j], hi);
+        lo = dp4a_uu(e, xc.le[j], lo);
+        lo = dp4a_uu(o, xc.lo[j], lo);
+    }
+    return hi * 256 + (lo - xc.xoff);
 }
 
 /* Sum of NV values over the 16 lanes of a half-warp; value i ends up in lane (16/NV)*i of the
- * half-warp (and its NV-1.. neighbours).  NV in {1, 2, 4}. */
+ * half-warp.  NV in {1, 2, 4}. */
 template <int NV>
 __device__ __forceinline__ float halfwarp_reduce(float (&v)[NV], int lane, unsigned mask) {
     float r;
@@ -247,8 +279,9 @@ struct Smem {
     uint64_t empty[kMaxStages];
     uint64_t part_full[kPartSlots];
     uint64_t part_empty[kPartSlots];
+    uint64_t x_full[2];
     int abort_flag;
-    int pad[15];
+    int pad[11];
     float part[kPartSlots][kPartFloats];
 };
 
@@ -261,16 +294,19 @@ __device__ __forceinline__ int cta_begin(int total, int cta, int ctas) {
     return (int)(((long long)total * cta) / ctas);
 }
 
+__device__ __forceinline__ void stamp(const FusedParams &P, int slot) {
+    if (P.trace && blockIdx.x == 0) P.trace[slot] = clock64();
+}
+
 /* ---- consumer side of one phase ------------------------------------------------------------ */
 template <int CIT, int MT, bool PAIRS>
-__device__ __forceinline__ void consume_phase(const PhasePlan &pl, const uint16_t *xsrc, Smem *sm,
-                                              uint8_t *ring, int stage_bytes, int nstages, int tile0,
-                                              unsigned *sync) {
+__device__ __forceinline__ void consume_phase(const FusedParams &P, const PhasePlan &pl, Smem *sm,
+                                              const uint16_t *xs, uint8_t *ring, int tile0) {
     constexpr int NVROW = (PAIRS ? 2 : 1) * MT;
-    constexpr int JTM = PAIRS ? 1 : kMaxJT; /* phase 1 tiles hold one pair per row group */
+    constexpr int JTM = PAIRS ? 2 : kMaxJT; /* row steps per thread per tile, upper bound */
+    const int stage_bytes = P.stage_bytes, nstages = P.nstages;
     const int ti = threadIdx.x - 32;
     const int lane = threadIdx.x & 31;
-    const int warp_lane0 = lane == 0;
     const bool active = ti < pl.CT * pl.RG;
     const int ct = ti % pl.CT, rg = ti / pl.CT;
     const unsigned hmask = 0xFFFFu << (lane & 16);
@@ -278,68 +314,41 @@ __device__ __forceinline__ void consume_phase(const PhasePlan &pl, const uint16_
     const int row_end = cta_begin(pl.rows_total, blockIdx.x + 1, gridDim.x);
     const int ntiles = (row_end - row_begin + pl.TR - 1) / pl.TR;
 
-    /* this thread's slice of the activation vector(s), in registers for the whole phase */
-    uint32_t xr[CIT][MT][16];
-    float xoff[CIT][MT];
+    /* this thread's slice of the activation vector(s): wait for it in shared memory, convert */
+    if (!mbar_wait(&sm->x_full[PAIRS ? 0 : 1], 0u, &sm->abort_flag)) {
+        give_up(sm, P.sync, ST_X_FULL);
+        return;
+    }
+    XChunk xc[CIT][MT];
 #pragma unroll
-    for (int m = 0; m < MT; ++m)
+    for (int c = 0; c < CIT; ++c)
 #pragma unroll
-        for (int c = 0; c < CIT; ++c) {
+        for (int m = 0; m < MT; ++m) {
             const int col = ct + c * pl.CT;
-            float sx = 0.0f;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (active && col < pl.cpr) v = ldg_cg16(xsrc + (size_t)m * pl.K + (size_t)col * 32 + q * 8);
-                xr[c][m][4 * q] = v.x; xr[c][m][4 * q + 1] = v.y; xr[c][m][4 * q + 2] = v.z; xr[c][m][4 * q + 3] = v.w;
-                sx += bf16_lo(v.x) + bf16_hi(v.x) + bf16_lo(v.y) + bf16_hi(v.y) + bf16_lo(v.z) + bf16_hi(v.z) +
-                      bf16_lo(v.w) + bf16_hi(v.w);
-            }
-            xoff[c][m] = 136.0f * sx;
+            prepare_chunk(xc[c][m], xs + (size_t)m * pl.K + (size_t)col * 32, active && col < pl.cpr);
         }
-
-    /* scales of the rows this thread will touch: one tile ahead, in registers */
-    uint16_t sc_next[JTM][PAIRS ? 2 : 1][CIT];
-    auto load_scales = [&](int lt) {
-        const int rows = min(pl.TR, row_end - (row_begin + lt * pl.TR));
-#pragma unroll
-        for (int j = 0; j < JTM; ++j) {
-            const int p = rg + j * pl.RG;
-            const bool on = active && j < pl.JT && p < rows;
-            const size_t r0 = (size_t)(row_begin + lt * pl.TR + p);
-#pragma unroll
-            for (int c = 0; c < CIT; ++c) {
-                const int col = ct + c * pl.CT;
-                const bool ok = on && col < pl.cpr;
-                sc_next[j][0][c] = ok ? __ldg(pl.s + r0 * pl.G + (col >> 2)) : (uint16_t)0;
-                if (PAIRS) sc_next[j][PAIRS ? 1 : 0][c] = ok ? __ldg(pl.s + (r0 + pl.up_offset) * pl.G + (col >> 2)) : (uint16_t)0;
-            }
-        }
-    };
-    if (ntiles > 0) load_scales(0);
+    if (threadIdx.x == 32) stamp(P, PAIRS ? 2 : 7);
 
     for (int lt = 0; lt < ntiles; ++lt) {
         const int tile = tile0 + lt;
         const int s = tile % nstages;
         const int rows = min(pl.TR, row_end - (row_begin + lt * pl.TR));
-        uint16_t sc[JTM][PAIRS ? 2 : 1][CIT];
-#pragma unroll
-        for (int j = 0; j < JTM; ++j)
-#pragma unroll
-            for (int h = 0; h < (PAIRS ? 2 : 1); ++h)
-#pragma unroll
-                for (int c = 0; c < CIT; ++c) sc[j][h][c] = sc_next[j][h][c];
-        if (lt + 1 < ntiles) load_scales(lt + 1);
-
         if (!mbar_wait(&sm->full[s], (uint32_t)(tile / nstages) & 1u, &sm->abort_flag)) {
-            give_up(sm, sync, ST_CONSUMER_FULL);
+            give_up(sm, P.sync, ST_CONSUMER_FULL);
             return;
         }
+        if (threadIdx.x == 32 && lt == 0) stamp(P, PAIRS ? 3 : 8);
         const uint8_t *st = ring + (size_t)s * stage_bytes;
+        /* the tile's scales sit behind its weights; the run starts where the global run does
+         * modulo 16 (the copy was widened down to a 16-byte boundary) */
+        const int row0 = row_begin + lt * pl.TR;
+        const uint16_t *sc0 = (const uint16_t *)(st + P.stage_w_bytes + (((size_t)row0 * pl.G * 2) & 15));
+        const uint16_t *sc1 = (const uint16_t *)(st + P.stage_w_bytes + P.sc_half_bytes +
+                                                 (((size_t)(row0 + pl.up_offset) * pl.G * 2) & 15));
         const int pslot = tile % kPartSlots;
         if (tile >= kPartSlots) { /* the epilogue must have drained this partial slot */
             if (!mbar_wait(&sm->part_empty[pslot], (uint32_t)(tile / kPartSlots - 1) & 1u, &sm->abort_flag)) {
-                give_up(sm, sync, ST_PART_EMPTY);
+                give_up(sm, P.sync, ST_PART_EMPTY);
                 return;
             }
         }
@@ -359,22 +368,16 @@ __device__ __forceinline__ void consume_phase(const PhasePlan &pl, const uint16_
                 const int col = ct + c * pl.CT;
                 if (col < pl.cpr) {
                     const uint4 w0 = lds16(st + (size_t)p * pl.rb + (size_t)col * 16);
-                    float d0[MT];
+                    const float s0 = bf16_bits_to_f32(sc0[p * pl.G + (col >> 2)]);
 #pragma unroll
-                    for (int m = 0; m < MT; ++m) d0[m] = 0.0f;
-                    chunk_dot<MT>(w0, xr[c], d0);
-                    const float s0 = bf16_bits_to_f32(sc[j][0][c]);
-#pragma unroll
-                    for (int m = 0; m < MT; ++m) val[m] = fmaf(s0, d0[m] - xoff[c][m], val[m]);
+                    for (int m = 0; m < MT; ++m)
+                        val[m] = fmaf((float)chunk_dot(w0, xc[c][m]), s0 * xc[c][m].fac, val[m]);
                     if (PAIRS) {
                         const uint4 w1 = lds16(st + (size_t)(rows + p) * pl.rb + (size_t)col * 16);
-                        float d1[MT];
+                        const float s1 = bf16_bits_to_f32(sc1[p * pl.G + (col >> 2)]);
 #pragma unroll
-                        for (int m = 0; m < MT; ++m) d1[m] = 0.0f;
-                        chunk_dot<MT>(w1, xr[c], d1);
-                        const float s1 = bf16_bits_to_f32(sc[j][PAIRS ? 1 : 0][c]);
-#pragma unroll
-                        for (int m = 0; m < MT; ++m) val[MT + m] = fmaf(s1, d1[m] - xoff[c][m], val[MT + m]);
+                        for (int m = 0; m < MT; ++m)
+                            val[MT + m] = fmaf((float)chunk_dot(w1, xc[c][m]), s1 * xc[c][m].fac, val[MT + m]);
                     }
                 }
             }
@@ -386,11 +389,12 @@ __device__ __forceinline__ void consume_phase(const PhasePlan &pl, const uint16_
             }
         }
         __syncwarp();
-        if (warp_lane0) {
+        if (lane == 0) {
             mbar_arrive(&sm->empty[s]);          /* the weight stage may be refilled */
             mbar_arrive(&sm->part_full[pslot]);  /* this warp's partials are in place */
         }
     }
+    if (threadIdx.x == 32) stamp(P, PAIRS ? 4 : 9);
 }
 
 /* ---- epilogue side of one phase ------------------------------------------------------------ */
@@ -444,14 +448,17 @@ template <int CIT1, int CIT2, int MT>
 __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParams P) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem *sm = (Smem *)smem_raw;
-    uint8_t *ring = smem_raw + ((sizeof(Smem) + 127) / 128) * 128;
+    uint16_t *xs = (uint16_t *)(smem_raw + ((sizeof(Smem) + 127) / 128) * 128);
+    uint8_t *ring = (uint8_t *)xs + P.xs_bytes;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ns = P.nstages;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < ns; ++s) { mbar_init(&sm->full[s], 1); mbar_init(&sm->empty[s], kConsumerWarps); }
-        for (int s = 0; s < kPartSlots; ++s) { mbar_init(&sm->part_full[s], kConsumerWarps); mbar_init(&sm->part_empty[s], 1); }
-        sm->abort_flag = 0;
+    if (warp == 0) {
+        if (lane == 0) stamp(P, 0);
+        if (lane < ns) { mbar_init(&sm->full[lane], 1); mbar_init(&sm->empty[lane], kConsumerWarps); }
+        if (lane >= 8 && lane < 8 + kPartSlots) { mbar_init(&sm->part_full[lane - 8], kConsumerWarps); mbar_init(&sm->part_empty[lane - 8], 1); }
+        if (lane >= 16 && lane < 18) mbar_init(&sm->x_full[lane - 16], 1);
+        if (lane == 31) sm->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -460,63 +467,98 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
     const int b2 = cta_begin(P.p2.rows_total, blockIdx.x, gridDim.x), e2 = cta_begin(P.p2.rows_total, blockIdx.x + 1, gridDim.x);
     const int nt1 = (e1 - b1 + P.p1.TR - 1) / P.p1.TR;
     const int nt2 = (e2 - b2 + P.p2.TR - 1) / P.p2.TR;
-    const unsigned my_gen = ld_acquire_gpu(P.sync + 1); /* grid-barrier generation at entry */
 
     if (warp == 0) {
         /* ---------------- producer ---------------- */
         if (lane == 0) {
-            int issued = 0;
-            for (int t = 0; t < nt1 + nt2; ++t) {
+            const unsigned my_gen = ld_acquire_gpu(P.sync + 1); /* grid-barrier generation at entry */
+            stamp(P, 1);
+            /* the activation vector of phase 1 */
+            mbar_expect_tx(&sm->x_full[0], (uint32_t)(P.M * P.H * 2));
+            bulk_g2s(xs, P.x, (uint32_t)(P.M * P.H * 2), &sm->x_full[0]);
+            const int total = nt1 + nt2;
+            int t = 0;
+            bool act_issued = false, failed = false;
+            /* Phase 2's activation vector is fetched once the grid barrier has opened (every CTA has
+             * stored its rows of act).  Phase 1's x is dead by then: this CTA's consumers finished
+             * phase 1 before its epilogue arrived at the barrier. */
+            auto fetch_act = [&]() {
+                bool open = false;
+                for (uint32_t i = 0; i < kSpinLimit && !open; ++i) {
+                    open = ld_acquire_gpu(P.sync + 1) != my_gen;
+                    if (!open) {
+                        if ((i & 63) == 63 && sm->abort_flag) break;
+                        __nanosleep(64);
+                    }
+                }
+                if (!open) { give_up(sm, P.sync, ST_GRID_BARRIER); failed = true; return; }
+                stamp(P, 6);
+                mbar_expect_tx(&sm->x_full[1], (uint32_t)(P.M * P.I * 2));
+                bulk_g2s(xs, P.act, (uint32_t)(P.M * P.I * 2), &sm->x_full[1]);
+                act_issued = true;
+            };
+            for (; t < total && !failed; ++t) {
                 const int s = t % ns;
+                /* A stage that still holds a phase-2 tile is only released after the consumers got
+                 * the activation vector, so that is the moment to go and wait for the barrier; a
+                 * stage holding a phase-1 tile frees up on its own. */
+                if (!act_issued && t - ns >= nt1) { fetch_act(); if (failed) break; }
                 if (t >= ns && !mbar_wait(&sm->empty[s], (uint32_t)(t / ns - 1) & 1u, &sm->abort_flag)) {
                     give_up(sm, P.sync, ST_PRODUCER_EMPTY);
+                    failed = true;
                     break;
                 }
                 uint8_t *dst = ring + (size_t)s * P.stage_bytes;
                 if (t < nt1) {
                     const int r0 = b1 + t * P.p1.TR, rows = min(P.p1.TR, e1 - r0);
                     const uint32_t bytes = (uint32_t)rows * P.p1.rb;
-                    mbar_expect_tx(&sm->full[s], 2 * bytes);
+                    /* scale runs widened to 16-byte boundaries (the array's end is one: row counts
+                     * are multiples of 8, so N*G*2 is a multiple of 16) */
+                    const size_t g0 = (size_t)r0 * P.p1.G * 2, g1 = (size_t)(r0 + P.p1.up_offset) * P.p1.G * 2;
+                    const size_t len = (size_t)rows * P.p1.G * 2;
+                    const size_t a0 = g0 & ~(size_t)15, a1 = g1 & ~(size_t)15;
+                    const uint32_t n0 = (uint32_t)(((g0 + len + 15) & ~(size_t)15) - a0);
+                    const uint32_t n1 = (uint32_t)(((g1 + len + 15) & ~(size_t)15) - a1);
+                    mbar_expect_tx(&sm->full[s], 2 * bytes + n0 + n1);
                     bulk_g2s(dst, P.p1.w + (size_t)r0 * P.p1.rb, bytes, &sm->full[s]);
                     bulk_g2s(dst + bytes, P.p1.w + (size_t)(r0 + P.p1.up_offset) * P.p1.rb, bytes, &sm->full[s]);
+                    bulk_g2s(dst + P.stage_w_bytes, (const uint8_t *)P.p1.s + a0, n0, &sm->full[s]);
+                    bulk_g2s(dst + P.stage_w_bytes + P.sc_half_bytes, (const uint8_t *)P.p1.s + a1, n1, &sm->full[s]);
                 } else {
                     const int r0 = b2 + (t - nt1) * P.p2.TR, rows = min(P.p2.TR, e2 - r0);
                     const uint32_t bytes = (uint32_t)rows * P.p2.rb;
-                    mbar_expect_tx(&sm->full[s], bytes);
+                    const size_t g0 = (size_t)r0 * P.p2.G * 2, len = (size_t)rows * P.p2.G * 2;
+                    const size_t a0 = g0 & ~(size_t)15;
+                    const uint32_t n0 = (uint32_t)(((g0 + len + 15) & ~(size_t)15) - a0);
+                    mbar_expect_tx(&sm->full[s], bytes + n0);
                     bulk_g2s(dst, P.p2.w + (size_t)r0 * P.p2.rb, bytes, &sm->full[s]);
+                    bulk_g2s(dst + P.stage_w_bytes, (const uint8_t *)P.p2.s + a0, n0, &sm->full[s]);
                 }
-                issued = t + 1;
             }
+            if (!act_issued && !failed) fetch_act();
             /* Never leave with a copy of ours still in flight: wait (bounded) for the most recent
-             * fill of every stage.  On the normal path the consumers have long seen them. */
-            for (int t = max(0, issued - ns); t < issued; ++t) {
+             * fill of every stage and for the activation copies. */
+            for (int u = max(0, t - ns); u < t; ++u) {
                 bool done = false;
-                for (uint32_t i = 0; i < kSpinLimit && !done; ++i) done = mbar_try_wait(&sm->full[t % ns], (uint32_t)(t / ns) & 1u);
+                for (uint32_t i = 0; i < kSpinLimit && !done; ++i) done = mbar_try_wait(&sm->full[u % ns], (uint32_t)(u / ns) & 1u);
+                if (!done) atomicCAS(P.sync + 3, 0u, (unsigned)ST_DRAIN | ((unsigned)blockIdx.x << 8));
+            }
+            for (int k = 0; k < (act_issued ? 2 : 1); ++k) {
+                bool done = false;
+                for (uint32_t i = 0; i < kSpinLimit && !done; ++i) done = mbar_try_wait(&sm->x_full[k], 0u);
                 if (!done) atomicCAS(P.sync + 3, 0u, (unsigned)ST_DRAIN | ((unsigned)blockIdx.x << 8));
             }
         }
     } else if (warp <= kConsumerWarps) {
         /* ---------------- consumers ---------------- */
-        consume_phase<CIT1, MT, true>(P.p1, P.x, sm, ring, P.stage_bytes, ns, 0, P.sync);
-        /* grid barrier: the whole activation vector must be in global memory before phase 2 */
-        if (threadIdx.x == 32) {
-            bool ok = false;
-            for (uint32_t i = 0; i < kSpinLimit; ++i) {
-                if (ld_acquire_gpu(P.sync + 1) != my_gen) { ok = true; break; }
-                if ((i & 255) == 255 && sm->abort_flag) break;
-                __nanosleep(20);
-            }
-            if (!ok) give_up(sm, P.sync, ST_GRID_BARRIER);
-        }
-        named_bar_sync(1, kConsumerThreads);
-        if (!sm->abort_flag)
-            consume_phase<CIT2, MT, false>(P.p2, P.act, sm, ring, P.stage_bytes, ns, nt1, P.sync);
+        consume_phase<CIT1, MT, true>(P, P.p1, sm, xs, ring, 0);
+        if (!sm->abort_flag) consume_phase<CIT2, MT, false>(P, P.p2, sm, xs, ring, nt1);
     } else {
         /* ---------------- epilogue ---------------- */
         /* read before this CTA arrives at the grid barrier: nobody can have advanced it yet */
         const unsigned seq = P.tp > 1 ? ld_acquire_gpu(P.sync + 2) : 0u;
         bool ok = epilogue_phase<MT, true>(P, P.p1, sm, 0, seq);
-        /* arrive at the grid barrier: act rows of this CTA are stored */
+        /* arrive at the grid barrier: the act rows of this CTA are stored */
         __syncwarp();
         if (lane == 0) {
             __threadfence();
@@ -526,8 +568,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
                 __threadfence();
                 atomicAdd(P.sync + 1, 1u); /* release everybody */
             }
+            stamp(P, 5);
         }
         if (ok) ok = epilogue_phase<MT, false>(P, P.p2, sm, nt1, seq);
+        if (lane == 0) stamp(P, 10);
         if (P.tp > 1) {
             /* publish this CTA's rows to every rank, wait for every rank's, add in rank order */
             __threadfence_system();
@@ -556,13 +600,16 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
                     P.out[(size_t)m * P.H + row] = f32_to_bf16_bits(y);
                 }
             }
+            if (lane == 0) stamp(P, 11);
         }
     }
     __syncthreads();
     /* the call sequence number advances once per launch (parity of the peer slots, flag target) */
-    if (blockIdx.x == 0 && threadIdx.x == 0 && P.tp > 1) atomicAdd(P.sync + 2, 1u);
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        if (P.tp > 1) atomicAdd(P.sync + 2, 1u);
+        stamp(P, 12);
+    }
 }
-
 
 /* ============================================================================================= */
 /* Host side: per-device state, the tiling plan, the launch                                      */
@@ -577,6 +624,9 @@ struct DeviceState {
     bool attr_set[2][2][2] = {};
 };
 static DeviceState g_dev[64];
+static long long *g_trace = nullptr; /* debugging aid: device buffer for CTA 0's clock stamps */
+
+void fused_set_trace(long long *device_buffer) { g_trace = device_buffer; }
 static std::mutex g_dev_mutex;
 
 static int device_state(DeviceState **out) {
@@ -606,7 +656,7 @@ static bool plan_phase(PhasePlan &pl, int K, int MT, bool pairs, int target_byte
     double best = -1.0;
     int best_cit = 0;
     for (int cit = 1; cit <= 2; ++cit) {
-        if (MT * cit > 2) continue; /* register budget: at most 32 activation registers */
+        if (MT * cit > 2) continue; /* register budget: at most two prepared activation chunks */
         const int ct = round_up((pl.cpr + cit - 1) / cit, 16);
         if (ct > kConsumerThreads) continue;
         int rg = kConsumerThreads / ct;
@@ -622,7 +672,7 @@ static bool plan_phase(PhasePlan &pl, int K, int MT, bool pairs, int target_byte
     pl.RG = kConsumerThreads / pl.CT;
     if (pairs) {
         pl.RG = min(pl.RG, max(1, target_bytes / (2 * pl.rb)));
-        pl.JT = 1;
+        pl.JT = max(1, min(2, target_bytes / (2 * pl.RG * pl.rb)));
     } else {
         pl.JT = max(1, min(kMaxJT, target_bytes / (pl.RG * pl.rb)));
     }
@@ -671,7 +721,8 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
         P.peer_slots = tp->peer_slots; P.peer_flags = tp->peer_flags; P.slot_stride = tp->slot_stride;
         if (tokens * H > tp->slot_stride) return fail(FFN_ERR_CONFIG, "fused FFN: %d tokens exceed the exchange buffer", tokens);
     }
-    const int target = 36 * 1024;
+    static const int target_kb = getenv("FFN_INT4_STAGE_KB") ? atoi(getenv("FFN_INT4_STAGE_KB")) : 62; /* tuning knob */
+    const int target = target_kb * 1024;
     int c1 = 0, c2 = 0;
     if (!plan_phase(P.p1, H, tokens, true, target, c1)) return FFN_NOT_ADMITTED;
     if (!plan_phase(P.p2, I, tokens, false, target, c2)) return FFN_NOT_ADMITTED;
@@ -681,8 +732,14 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
     P.p2.rows_total = H; P.p2.up_offset = 0;
     if (P.p1.TR * 2 * tokens * P.p1.nhw > kPartFloats || P.p2.TR * tokens * P.p2.nhw > kPartFloats)
         return FFN_NOT_ADMITTED;
-    P.stage_bytes = round_up(max(2 * P.p1.TR * P.p1.rb, P.p2.TR * P.p2.rb), 128);
-    const size_t fixed = ((sizeof(Smem) + 127) / 128) * 128;
+    if (((uintptr_t)w->gate_up_i4_scales & 15) || ((uintptr_t)w->down_i4_scales & 15)) return FFN_NOT_ADMITTED;
+    P.stage_w_bytes = round_up(max(2 * P.p1.TR * P.p1.rb, P.p2.TR * P.p2.rb), 128);
+    P.sc_half_bytes = round_up(max(P.p1.TR * P.p1.G * 2, P.p2.TR * P.p2.G * 2) + 32, 16);
+    P.stage_bytes = round_up(P.stage_w_bytes + 2 * P.sc_half_bytes, 128);
+    P.xs_bytes = round_up(tokens * max(H, I) * 2, 128);
+    P.trace = g_trace;
+    const size_t fixed = ((sizeof(Smem) + 127) / 128) * 128 + (size_t)P.xs_bytes;
+    if (fixed + 2 * (size_t)P.stage_bytes > (size_t)d.smem_optin) return FFN_NOT_ADMITTED;
     P.nstages = (int)min((size_t)kMaxStages, ((size_t)d.smem_optin - fixed) / (size_t)P.stage_bytes);
     if (P.nstages < 2) return FFN_NOT_ADMITTED;
     const size_t smem = fixed + (size_t)P.nstages * P.stage_bytes;

@@ -41,5 +41,6 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
  * 0 = fine, else (where | cta << 8).  With reset, a non-zero status also clears the kernel's
  * synchronisation words so the next launch starts clean. */
 int fused_status(unsigned *status_out, bool reset);
+void fused_set_trace(long long *device_buffer);
 
 }  // namespace ffn

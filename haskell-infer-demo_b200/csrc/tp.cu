@@ -1,0 +1,195 @@
+/*
+ * tp.cu - tensor-parallel plumbing of the fused FFN: the per-rank exchange buffer the down
+ * projection's epilogue writes into on every peer, how ranks learn each other's buffers (CUDA IPC
+ * between processes, peer access inside one process), and the operator entry that runs one rank's
+ * FFN with the in-kernel reduce.  Replaces the reference's peer_probe_all / allreduce_sum pair
+ * (csrc/collective.cu:108-144, 168-219) for this path: no staging copies, no host-issued adds.
+ *
+ * One exchange buffer per rank, one allocation:
+ *     [ flags: kTpMaxCtas x u32 | pad to 1 KiB | slots: 2 x tp x max_tokens*hidden x f32 ]
+ * flags[c] counts arrivals of "CTA c" from every rank (monotonic; the kernel derives its target from
+ * a device-resident call counter, so replaying a captured graph stays correct).  Slots are double
+ * buffered by call parity: a rank can be at most one call ahead of a peer, because completing a
+ * call needs every peer's flag increment for that call.
+ */
+#include <string.h>
+
+#include <new>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ffn {
+
+constexpr int kTpMaxCtas = 256;
+constexpr int kTpMaxRanks = 16;
+constexpr size_t kTpFlagBytes = 1024;
+
+struct TpComm {
+    int tp = 0, rank = 0, hidden = 0, max_tokens = 0, device = 0;
+    size_t bytes = 0;
+    uint8_t *local = nullptr;             /* this rank's exchange buffer */
+    uint8_t *peer[kTpMaxRanks] = {};      /* every rank's buffer as seen from this device */
+    bool opened[kTpMaxRanks] = {};        /* peer[r] came from cudaIpcOpenMemHandle */
+    float **d_slots = nullptr;            /* device arrays handed to the kernel */
+    unsigned **d_flags = nullptr;
+    bool connected = false;
+};
+
+static int tp_publish_tables(TpComm *c) {
+    float *slots[kTpMaxRanks];
+    unsigned *flags[kTpMaxRanks];
+    for (int r = 0; r < c->tp; ++r) {
+        flags[r] = (unsigned *)c->peer[r];
+        slots[r] = (float *)(c->peer[r] + kTpFlagBytes);
+    }
+    if (!c->d_slots && cudaMalloc(&c->d_slots, sizeof(slots)) != cudaSuccess)
+        return fail(FFN_ERR_ALLOC, "ffn_tp: cannot allocate the peer table");
+    if (!c->d_flags && cudaMalloc(&c->d_flags, sizeof(flags)) != cudaSuccess)
+        return fail(FFN_ERR_ALLOC, "ffn_tp: cannot allocate the peer table");
+    FFN_CUDA_TRY(cudaMemcpy(c->d_slots, slots, sizeof(slots), cudaMemcpyHostToDevice), "ffn_tp: peer table");
+    FFN_CUDA_TRY(cudaMemcpy(c->d_flags, flags, sizeof(flags), cudaMemcpyHostToDevice), "ffn_tp: peer table");
+    c->connected = true;
+    return FFN_OK;
+}
+
+}  // namespace ffn
+
+using namespace ffn;
+
+extern "C" {
+
+int ffn_tp_create(FfnTpComm **out, int tp, int rank, int hidden, int max_tokens) {
+    clear_error();
+    if (!out) return fail(FFN_ERR_CONFIG, "ffn_tp_create: null argument");
+    if (tp < 1 || tp > kTpMaxRanks || rank < 0 || rank >= tp)
+        return fail(FFN_ERR_CONFIG, "ffn_tp_create: rank %d is outside [0, %d) or more than %d ranks", rank, tp, kTpMaxRanks);
+    if (hidden <= 0 || hidden % FFN_INT4_GROUP || max_tokens < 1)
+        return fail(FFN_ERR_CONFIG, "ffn_tp_create: invalid hidden size or token bound");
+    TpComm *c = new (std::nothrow) TpComm();
+    if (!c) return fail(FFN_ERR_ALLOC, "ffn_tp_create: out of host memory");
+    c->tp = tp; c->rank = rank; c->hidden = hidden; c->max_tokens = max_tokens;
+    if (cudaGetDevice(&c->device) != cudaSuccess) { delete c; return fail(FFN_ERR_CUDA, "ffn_tp_create: no CUDA device"); }
+    c->bytes = kTpFlagBytes + (size_t)2 * tp * max_tokens * hidden * sizeof(float);
+    if (cudaMalloc(&c->local, c->bytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        delete c;
+        return fail(FFN_ERR_ALLOC, "ffn_tp_create: cannot allocate the %zu-byte exchange buffer", c->bytes);
+    }
+    if (cudaMemset(c->local, 0, c->bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+        cudaFree(c->local);
+        delete c;
+        return fail(FFN_ERR_CUDA, "ffn_tp_create: cannot clear the exchange buffer");
+    }
+    c->peer[rank] = c->local;
+    *out = (FfnTpComm *)c;
+    if (tp == 1) return tp_publish_tables(c);
+    return FFN_OK;
+}
+
+int ffn_tp_export(FfnTpComm *comm, void *handle_out) {
+    clear_error();
+    TpComm *c = (TpComm *)comm;
+    if (!c || !handle_out) return fail(FFN_ERR_CONFIG, "ffn_tp_export: null argument");
+    cudaIpcMemHandle_t h;
+    FFN_CUDA_TRY(cudaIpcGetMemHandle(&h, c->local), "ffn_tp_export: cudaIpcGetMemHandle");
+    static_assert(sizeof(h) == FFN_TP_HANDLE_BYTES, "IPC handle size");
+    memcpy(handle_out, &h, sizeof(h));
+    return FFN_OK;
+}
+
+int ffn_tp_connect(FfnTpComm *comm, const void *all_handles) {
+    clear_error();
+    TpComm *c = (TpComm *)comm;
+    if (!c || !all_handles) return fail(FFN_ERR_CONFIG, "ffn_tp_connect: null argument");
+    if (c->connected) return fail(FFN_ERR_STATE, "ffn_tp_connect: already connected");
+    FFN_CUDA_TRY(cudaSetDevice(c->device), "ffn_tp_connect: select device");
+    for (int r = 0; r < c->tp; ++r) {
+        if (r == c->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t *)all_handles + (size_t)r * FFN_TP_HANDLE_BYTES, sizeof(h));
+        void *p = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            return fail(FFN_ERR_CUDA, "ffn_tp_connect: rank %d cannot map rank %d's exchange buffer: %s", c->rank, r,
+                        cudaGetErrorString(e));
+        }
+        c->peer[r] = (uint8_t *)p;
+        c->opened[r] = true;
+    }
+    return tp_publish_tables(c);
+}
+
+int ffn_tp_connect_local(FfnTpComm *const *comms, int count) {
+    clear_error();
+    if (!comms || count < 1 || count > kTpMaxRanks) return fail(FFN_ERR_CONFIG, "ffn_tp_connect_local: bad arguments");
+    for (int i = 0; i < count; ++i) {
+        TpComm *c = (TpComm *)comms[i];
+        if (!c || c->tp != count || c->rank != i) return fail(FFN_ERR_CONFIG, "ffn_tp_connect_local: element %d is not rank %d of %d", i, i, count);
+    }
+    int restore = 0;
+    (void)cudaGetDevice(&restore);
+    for (int i = 0; i < count; ++i) {
+        TpComm *c = (TpComm *)comms[i];
+        FFN_CUDA_TRY(cudaSetDevice(c->device), "ffn_tp_connect_local: select device");
+        for (int j = 0; j < count; ++j) {
+            TpComm *o = (TpComm *)comms[j];
+            c->peer[j] = o->local;
+            if (i == j || o->device == c->device) continue;
+            int can = 0;
+            FFN_CUDA_TRY(cudaDeviceCanAccessPeer(&can, c->device, o->device), "ffn_tp_connect_local: peer query");
+            if (!can) return fail(FFN_ERR_CONFIG, "ffn_tp_connect_local: device %d cannot reach device %d", c->device, o->device);
+            const cudaError_t e = cudaDeviceEnablePeerAccess(o->device, 0);
+            if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled)
+                return fail(FFN_ERR_CUDA, "ffn_tp_connect_local: peer access %d->%d: %s", c->device, o->device, cudaGetErrorString(e));
+            (void)cudaGetLastError(); /* "already enabled" is sticky (csrc/collective.cu:127-131) */
+        }
+        const int st = tp_publish_tables(c);
+        if (st) return st;
+    }
+    (void)cudaSetDevice(restore);
+    return FFN_OK;
+}
+
+int ffn_tp_destroy(FfnTpComm *comm) {
+    clear_error();
+    TpComm *c = (TpComm *)comm;
+    if (!c) return FFN_OK;
+    (void)cudaSetDevice(c->device);
+    (void)cudaDeviceSynchronize();
+    for (int r = 0; r < c->tp; ++r)
+        if (c->opened[r]) (void)cudaIpcCloseMemHandle(c->peer[r]);
+    if (c->d_slots) cudaFree(c->d_slots);
+    if (c->d_flags) cudaFree(c->d_flags);
+    if (c->local) cudaFree(c->local);
+    delete c;
+    (void)cudaGetLastError();
+    return FFN_OK;
+}
+
+int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *ws, void *layer_out,
+                       const FfnMlpWeights *w, int tokens, const FfnModelDims *dims, void *residual) {
+    clear_error();
+    TpComm *c = (TpComm *)comm;
+    if (!c || !w || !dims || !normed || !ws || !layer_out) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: null argument");
+    if (!c->connected) return fail(FFN_ERR_STATE, "ffn_forward_mlp_tp: the communicator is not connected");
+    if (dims->hidden_size != c->hidden) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: hidden size %d, communicator built for %d", dims->hidden_size, c->hidden);
+    if (tokens < 1 || tokens > c->max_tokens) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: %d tokens, communicator built for at most %d", tokens, c->max_tokens);
+    if (!w->gate_up_i4 || !w->gate_up_i4_scales || !w->down_i4 || !w->down_i4_scales || w->i4_group != FFN_INT4_GROUP)
+        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: the layer carries no INT4 operands");
+    const int H = dims->hidden_size, I = dims->intermediate_size;
+    if (I <= 0 || I % FFN_INT4_GROUP) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: the rank's intermediate size %d splits K at a non-group boundary", I);
+    FusedTp t;
+    t.tp = c->tp; t.rank = c->rank;
+    t.peer_slots = c->d_slots; t.peer_flags = c->d_flags;
+    t.slot_stride = c->max_tokens * c->hidden;
+    t.max_ctas = kTpMaxCtas;
+    uint16_t *act = (uint16_t *)ws + (size_t)tokens * H + (size_t)2 * tokens * I;
+    const int st = fused_ffn_launch((cudaStream_t)stream, normed, act, layer_out, w, tokens, H, I, &t, residual);
+    if (st == FFN_NOT_ADMITTED)
+        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: the fused kernel does not take this shape (tokens=%d H=%d I=%d)", tokens, H, I);
+    return st;
+}
+
+}  // extern "C"

@@ -56,10 +56,18 @@ def _declare(lib):
         "ffn_forward_mlp": [vp, vp, vp, vp, vp, ctypes.POINTER(MlpWeights), ci, ctypes.POINTER(ModelDims)],
         "ffn_forward_mlp_prepared": [vp, vp, vp, vp, vp, ctypes.POINTER(MlpWeights), ci,
                                      ctypes.POINTER(ModelDims)],
+        "ffn_tp_create": [ctypes.POINTER(vp), ci, ci, ci, ci],
+        "ffn_tp_export": [vp, vp],
+        "ffn_tp_connect": [vp, vp],
+        "ffn_tp_connect_local": [ctypes.POINTER(vp), ci],
+        "ffn_tp_destroy": [vp],
+        "ffn_forward_mlp_tp": [vp, vp, vp, vp, vp, ctypes.POINTER(MlpWeights), ci, ctypes.POINTER(ModelDims), vp],
         "test_gemm_int4": [vp, vp, vp, vp, ci, ci, ci, ci],
         "test_silu_mul_packed": [vp, vp, ci, ci],
         "test_norm": [vp, vp, vp, ci, ci],
     }
+    lib.ffn_int4_debug_trace.argtypes = [vp]
+    lib.ffn_int4_debug_trace.restype = None
     for name, args in sigs.items():
         fn = getattr(lib, name)
         fn.argtypes = args

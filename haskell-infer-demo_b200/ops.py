@@ -122,3 +122,64 @@ class DenseMlp:
                                               ctypes.byref(self.weights), tokens,
                                               ctypes.byref(self.dims)))
         return layer_out
+
+
+class TpComm:
+    """One rank's end of the in-kernel cross-rank reduce (include/ffn_int4.h, ffn_tp_*).
+
+    ``TpComm.over_process_group(hidden, max_tokens)`` is the one-process-per-GPU form: each rank
+    allocates its exchange buffer, the CUDA IPC handles travel through torch.distributed, and every
+    rank maps every peer's buffer.  ``TpComm.local(devices, ...)`` is the reference's process model
+    (one process drives every rank) and returns one communicator per device.
+    """
+
+    def __init__(self, handle, tp, rank):
+        self.handle, self.tp, self.rank = handle, tp, rank
+
+    @staticmethod
+    def _create(tp, rank, hidden, max_tokens):
+        h = ctypes.c_void_p()
+        check(load().ffn_tp_create(ctypes.byref(h), tp, rank, hidden, max_tokens))
+        return TpComm(h, tp, rank)
+
+    @classmethod
+    def over_process_group(cls, hidden, max_tokens, group=None):
+        import torch.distributed as dist
+        tp, rank = dist.get_world_size(group), dist.get_rank(group)
+        comm = cls._create(tp, rank, hidden, max_tokens)
+        if tp > 1:
+            mine = (ctypes.c_uint8 * 64)()
+            check(load().ffn_tp_export(comm.handle, mine))
+            gathered = [None] * tp
+            dist.all_gather_object(gathered, bytes(mine), group=group)
+            blob = b"".join(gathered)
+            check(load().ffn_tp_connect(comm.handle, ctypes.c_char_p(blob)))
+            dist.barrier(group)
+        return comm
+
+    @classmethod
+    def local(cls, devices, hidden, max_tokens):
+        comms = []
+        for r, d in enumerate(devices):
+            with torch.cuda.device(d):
+                comms.append(cls._create(len(devices), r, hidden, max_tokens))
+        if len(devices) > 1:
+            arr = (ctypes.c_void_p * len(devices))(*[c.handle for c in comms])
+            check(load().ffn_tp_connect_local(arr, len(devices)))
+        return comms
+
+    def forward_mlp(self, mlp, normed, ws=None, layer_out=None, residual=None):
+        """``mlp`` holds this rank's slice (see DenseMlp); returns the reduced bf16 [T, H]."""
+        tokens = normed.shape[0]
+        ws = mlp.workspace(tokens) if ws is None else ws
+        layer_out = torch.empty((tokens, mlp.hidden), dtype=torch.bfloat16,
+                                device=mlp.device) if layer_out is None else layer_out
+        check(load().ffn_forward_mlp_tp(self.handle, _stream(), _ptr(normed), _ptr(ws), _ptr(layer_out),
+                                        ctypes.byref(mlp.weights), tokens, ctypes.byref(mlp.dims),
+                                        _ptr(residual)))
+        return layer_out
+
+    def close(self):
+        if self.handle:
+            load().ffn_tp_destroy(self.handle)
+            self.handle = None

@@ -46,10 +46,15 @@ int ffn_int4_abi_version(void);
 /* Synchronises the current device and reports whether any fused kernel since the last call gave
  * up on a bounded wait (every device-side wait in this library has an iteration limit; on expiry
  * the kernel records where and returns instead of hanging).  Returns FFN_OK, or FFN_ERR_CUDA with
- * `where` (1..7) and `cta` filled; a non-zero status is cleared and the kernel's synchronisation
+ * `where` (1..8) and `cta` filled; a non-zero status is cleared and the kernel's synchronisation
  * words are reset, the analogue of the reference's "failed forward needs engine_reset"
  * (csrc/engine.cu:1723-1730).  No counterpart function in the reference. */
 int ffn_int4_device_status(int *where, int *cta);
+
+/* Debugging aid: when given a device buffer of 16 int64, CTA 0 of every later fused launch writes
+ * clock64() stamps of its pipeline events there (NULL switches it off).  No counterpart in the
+ * reference (its profiler times whole regions with events, csrc/profile.cu:114-144). */
+void ffn_int4_debug_trace(void *device_buffer);
 
 /* Chooses between the single-launch fused FFN kernel (default, 1) and the three-kernel route
  * (gate/up GEMM, SiLU*up, down GEMM - the reference's launch structure, csrc/kernels/layers.cu:
@@ -152,6 +157,40 @@ int ffn_forward_mlp(void *cublas, void *stream, const void *residual, void *ws, 
 int ffn_forward_mlp_prepared(void *cublas, void *stream, const void *normed, void *ws,
                              void *layer_out, const FfnMlpWeights *w, int tokens,
                              const FfnModelDims *dims);
+
+/* ------------------------------------------------------------------------------------------- */
+/* Tensor parallelism: the down projection's partial sums are reduced across ranks from inside    */
+/* the FFN kernel (peer stores over NVLink), replacing allreduce_sum on the layer output           */
+/* (csrc/include/layers.h:303-305; csrc/collective.cu:168-219; caller csrc/engine.cu:1436-1452)    */
+/* and peer_probe_all (csrc/collective.cu:108-144).                                                */
+/* ------------------------------------------------------------------------------------------- */
+typedef struct FfnTpComm FfnTpComm;
+#define FFN_TP_HANDLE_BYTES 64
+
+/* Allocates this rank's exchange buffer on the current device (flags + 2*tp*max_tokens*hidden FP32
+ * slots, zeroed).  One communicator per rank; rank order is device-list order as in the reference
+ * (csrc/engine.cu:997-1011). */
+int ffn_tp_create(FfnTpComm **out, int tp, int rank, int hidden, int max_tokens);
+/* One process per rank: export this rank's buffer (FFN_TP_HANDLE_BYTES bytes), exchange the handles
+ * by any host channel, then connect with all tp handles in rank order (own entry ignored). */
+int ffn_tp_export(FfnTpComm *comm, void *handle_out);
+int ffn_tp_connect(FfnTpComm *comm, const void *all_handles);
+/* One process driving every rank (the reference's process model, csrc/include/engine.h:8-9): enables
+ * peer access between the communicators' devices and wires them up.  comms[i] must be rank i. */
+int ffn_tp_connect_local(FfnTpComm *const *comms, int count);
+int ffn_tp_destroy(FfnTpComm *comm);
+
+/* One rank's FFN with the cross-rank reduce fused into the kernel: normed [tokens][H] (replicated on
+ * every rank) -> layer_out [tokens][H] = bf16(sum over ranks of the FP32 down partials), identical on
+ * every rank (partials are added in rank order).  `w`/`dims` describe the RANK-LOCAL operands
+ * (gate/up [2*I/R][H], down [H][I/R], intermediate_size = I/R) exactly as the reference's per-rank
+ * MlpWeights do.  `ws` as for ffn_forward_mlp.  If `residual` is non-NULL the kernel also applies
+ * residual = bf16(f32(residual) + f32(layer_out)) (residual_add_device, csrc/engine.cu:1428-1433).
+ * Every rank must make the same sequence of calls; a rank that never launches makes the others
+ * return after a bounded wait with a status ffn_int4_device_status reports.  Token counts the fused
+ * kernel does not take (currently > 2) are refused with FFN_ERR_CONFIG. */
+int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *ws, void *layer_out,
+                       const FfnMlpWeights *w, int tokens, const FfnModelDims *dims, void *residual);
 
 /* ------------------------------------------------------------------------------------------- */
 /* The reference's kernel test bridge (tests/kernels/kernel_bridge.cu), same names and           */
