@@ -50,8 +50,7 @@ constexpr int kMaxStages = 8;
 constexpr int kPartSlots = 4;
 constexpr int kPartFloats = 512;                       /* floats per partial slot */
 constexpr int kMaxJT = 4;                              /* row steps per thread per tile */
-constexpr uint32_t kSpinLimit = 1u << 24;              /* bounded waits: ~1 s worst case */
-constexpr int kTraceWords = 16;
+constexpr uint32_t kSpinLimit = 1u << 22;              /* bounded waits: polls of >= 32..100 ns, i.e. 0.15 .. 0.5 s */
 
 /* status word values (where a wait gave up) */
 enum { ST_OK = 0, ST_PRODUCER_EMPTY = 1, ST_CONSUMER_FULL = 2, ST_PART_EMPTY = 3, ST_PART_FULL = 4,
@@ -76,7 +75,8 @@ struct FusedParams {
     int stage_bytes, nstages, xs_bytes;
     int stage_w_bytes;    /* weights part of a stage; the tile's scales follow it */
     int sc_half_bytes;    /* room for one contiguous run of scales (gate or up) incl. 16 bytes of slack */
-    unsigned *sync;       /* [0] arrival count, [1] generation, [2] call sequence, [3] status */
+    unsigned *sync;       /* [0] arrivals (monotonic), [1] arrivals at the end of the previous launch,
+                             [2] call sequence, [3] status */
     /* tensor parallelism (tp == 1: unused) */
     int tp, rank;
     float *const *peer_slots;   /* device array [tp]: each rank's [2][tp][M_max][H] fp32 slots */
@@ -85,6 +85,7 @@ struct FusedParams {
     /* optional fused residual update on the reduced output (h <- bf16(h + y)); NULL = off */
     uint16_t *residual;
     long long *trace;     /* optional [kTraceWords] clock64 stamps of CTA 0 (NULL = off) */
+    int debug;            /* measurement aid: bit 0 skips the arithmetic, bit 1 skips the weight copies */
 };
 
 /* ---- PTX wrappers -------------------------------------------------------------------------- */
@@ -110,17 +111,33 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-/* Bounded wait.  Returns false when the limit ran out or another thread already gave up. */
+/* Bounded wait.  Returns false when the limit ran out or another thread already gave up.  A
+ * waiting warp sleeps between polls so that it does not take issue slots from the arithmetic
+ * warps: SLEEP_NS is short for the consumers (they wait for data) and longer for the producer and
+ * the epilogue, which wait most of the time. */
+template <int SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        __nanosleep(SLEEP_NS);
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023) == 1023 && *abort_flag) return false;
+        if ((i & 255) == 255 && *abort_flag) return false;
     }
     return false;
 }
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint4 lds16_at(uint32_t addr) { /* addr: shared-window byte address */
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float lds_bf16_at(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return __uint_as_float((uint32_t)v << 16);
 }
 __device__ __forceinline__ uint4 lds16(const void *p) {
     uint4 v;
@@ -150,14 +167,14 @@ __device__ __forceinline__ uint32_t lop3_and_xor(uint32_t a, uint32_t b, uint32_
     asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); /* (a & b) ^ c */
     return d;
 }
-__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) { /* unsigned bytes x signed bytes */
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) { /* signed bytes x signed bytes */
     int d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c) { /* unsigned x unsigned */
+__device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c) { /* signed bytes x unsigned bytes */
     int d;
-    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -174,10 +191,9 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
  * dp4a against the widened weight bytes: word j (codes k = 8j..8j+7) pairs
  *   even codes k = 8j + {0,2,4,6}  with  he[j] (high bytes, signed) and le[j] (low bytes, unsigned)
  *   odd  codes k = 8j + {1,3,5,7}  with  ho[j] / lo[j].
- * xoff = 8 * sum(X) removes the +8 offset the widened codes carry; fac = 2^(E-14) undoes the scaling. */
+ * fac = 2^(E-14) / 16 undoes the scaling of X and the factor 16 the widened codes carry. */
 struct XChunk {
     uint32_t he[4], ho[4], le[4], lo[4];
-    int xoff;
     float fac;
 };
 
@@ -194,18 +210,19 @@ __device__ __forceinline__ void prepare_chunk(XChunk &xc, const uint16_t *src /*
     for (int i = 0; i < 16; ++i) mx = __vmaxu2(mx, v[i] & 0x7FFF7FFFu);
     const uint32_t top = max(mx & 0xFFFFu, mx >> 16);
     const int E = (int)(top >> 7); /* biased exponent of the largest magnitude */
-    /* E < 15 (|x| < 2^-112) is treated as an all-zero slice; Inf/NaN inputs are outside the contract */
-    const bool live = E >= 15 && E < 255;
+    /* E < 19 (|x| < 2^-108) is treated as an all-zero slice; Inf/NaN inputs are outside the contract */
+    const bool live = E >= 19 && E < 255;
     const float up = live ? __uint_as_float((uint32_t)(268 - E) << 23) : 0.0f;   /* 2^(141-E) */
-    xc.fac = live ? __uint_as_float((uint32_t)(E - 14) << 23) : 0.0f;            /* 2^(E-141) */
-    int total_hi = 0, total_lo = 0;
+    xc.fac = live ? __uint_as_float((uint32_t)(E - 18) << 23) : 0.0f;            /* 2^(E-141) / 16 */
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         int X[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            X[2 * i] = __float2int_rn(bf16_lo(v[4 * j + i]) * up);
-            X[2 * i + 1] = __float2int_rn(bf16_hi(v[4 * j + i]) * up);
+            /* 1.5*2^23 + x*up has the rounded (nearest-even) integer in its low mantissa bits; only
+             * the low 16 bits are used below and 0x4B400000 contributes none of them */
+            X[2 * i] = __float_as_int(fmaf(bf16_lo(v[4 * j + i]), up, 12582912.0f));
+            X[2 * i + 1] = __float_as_int(fmaf(bf16_hi(v[4 * j + i]), up, 12582912.0f));
         }
         /* bytes 0/1 of each X are its low/high byte (two's complement 16-bit) */
         const uint32_t e02 = prmt(X[0], X[2], 0x5140), e46 = prmt(X[4], X[6], 0x5140); /* lo0 lo2 hi0 hi2 */
@@ -214,29 +231,26 @@ __device__ __forceinline__ void prepare_chunk(XChunk &xc, const uint16_t *src /*
         xc.he[j] = prmt(e02, e46, 0x7632);
         xc.lo[j] = prmt(o13, o57, 0x5410);
         xc.ho[j] = prmt(o13, o57, 0x7632);
-        total_hi = dp4a_us(0x01010101u, xc.he[j], total_hi);
-        total_hi = dp4a_us(0x01010101u, xc.ho[j], total_hi);
-        total_lo = dp4a_uu(0x01010101u, xc.le[j], total_lo);
-        total_lo = dp4a_uu(0x01010101u, xc.lo[j], total_lo);
     }
-    xc.xoff = 8 * (total_hi * 256 + total_lo);
 }
 
-/* sum_k code_k * X_k over one 16-byte chunk, exact. (w & 0x0F0F0F0F) ^ 0x08080808 widens the even
- * nibbles of a word to bytes holding code+8 in [1,15]; the shifted word gives the odd nibbles. */
+/* 16 * sum_k code_k * X_k over one 16-byte chunk.  A 4-bit two's-complement code placed in the high
+ * nibble of a byte IS the signed byte 16*code, so (w & 0xF0F0F0F0) holds the odd codes of a word
+ * and ((w << 4) & 0xF0F0F0F0) the even ones, ready for a signed dp4a: one shift and two ANDs widen
+ * eight codes, with no offset to remove afterwards.  Integer arithmetic, exact (|sum| < 2^27). */
 __device__ __forceinline__ int chunk_dot(const uint4 &w, const XChunk &xc) {
     int hi = 0, lo = 0;
     const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        const uint32_t e = lop3_and_xor(ws[j], 0x0F0F0F0Fu, 0x08080808u);
-        const uint32_t o = lop3_and_xor(ws[j] >> 4, 0x0F0F0F0Fu, 0x08080808u);
-        hi = dp4a_us(e, xc.he[j], hi);
-        hi = dp4a_us(o, xc.ho[j], hi);
-        lo = dp4a_uu(e, xc.le[j], lo);
-        lo = dp4a_uu(o, xc.lo[j], lo);
+        const uint32_t o = ws[j] & 0xF0F0F0F0u;
+        const uint32_t e = (ws[j] << 4) & 0xF0F0F0F0u;
+        hi = dp4a_ss(e, xc.he[j], hi);
+        hi = dp4a_ss(o, xc.ho[j], hi);
+        lo = dp4a_su(e, xc.le[j], lo);
+        lo = dp4a_su(o, xc.lo[j], lo);
     }
-    return hi * 256 + (lo - xc.xoff);
+    return hi * 256 + lo;
 }
 
 /* Sum of NV values over the 16 lanes of a half-warp; value i ends up in lane (16/NV)*i of the
@@ -303,8 +317,9 @@ template <int CIT, int MT, bool PAIRS>
 __device__ __forceinline__ void consume_phase(const FusedParams &P, const PhasePlan &pl, Smem *sm,
                                               const uint16_t *xs, uint8_t *ring, int tile0) {
     constexpr int NVROW = (PAIRS ? 2 : 1) * MT;
-    constexpr int JTM = PAIRS ? 2 : kMaxJT; /* row steps per thread per tile, upper bound */
+    constexpr int JTM = 4 / NVROW; /* row steps per thread per tile: four values per reduction */
     const int stage_bytes = P.stage_bytes, nstages = P.nstages;
+    const uint32_t ring_addr = smem_u32(ring);
     const int ti = threadIdx.x - 32;
     const int lane = threadIdx.x & 31;
     const bool active = ti < pl.CT * pl.RG;
@@ -315,7 +330,7 @@ __device__ __forceinline__ void consume_phase(const FusedParams &P, const PhaseP
     const int ntiles = (row_end - row_begin + pl.TR - 1) / pl.TR;
 
     /* this thread's slice of the activation vector(s): wait for it in shared memory, convert */
-    if (!mbar_wait(&sm->x_full[PAIRS ? 0 : 1], 0u, &sm->abort_flag)) {
+    if (!mbar_wait<100>(&sm->x_full[PAIRS ? 0 : 1], 0u, &sm->abort_flag)) {
         give_up(sm, P.sync, ST_X_FULL);
         return;
     }
@@ -333,59 +348,78 @@ __device__ __forceinline__ void consume_phase(const FusedParams &P, const PhaseP
         const int tile = tile0 + lt;
         const int s = tile % nstages;
         const int rows = min(pl.TR, row_end - (row_begin + lt * pl.TR));
-        if (!mbar_wait(&sm->full[s], (uint32_t)(tile / nstages) & 1u, &sm->abort_flag)) {
+        if (!mbar_wait<32>(&sm->full[s], (uint32_t)(tile / nstages) & 1u, &sm->abort_flag)) {
             give_up(sm, P.sync, ST_CONSUMER_FULL);
             return;
         }
         if (threadIdx.x == 32 && lt == 0) stamp(P, PAIRS ? 3 : 8);
-        const uint8_t *st = ring + (size_t)s * stage_bytes;
-        /* the tile's scales sit behind its weights; the run starts where the global run does
-         * modulo 16 (the copy was widened down to a 16-byte boundary) */
+        /* 32-bit shared-window addresses from here on.  The tile's scales sit behind its weights;
+         * a run starts where the global run does modulo 16 (the copy was widened down to a 16-byte
+         * boundary). */
         const int row0 = row_begin + lt * pl.TR;
-        const uint16_t *sc0 = (const uint16_t *)(st + P.stage_w_bytes + (((size_t)row0 * pl.G * 2) & 15));
-        const uint16_t *sc1 = (const uint16_t *)(st + P.stage_w_bytes + P.sc_half_bytes +
-                                                 (((size_t)(row0 + pl.up_offset) * pl.G * 2) & 15));
+        const uint32_t st = ring_addr + (uint32_t)s * (uint32_t)stage_bytes;
+        const uint32_t sc0 = st + (uint32_t)P.stage_w_bytes + (((uint32_t)row0 * (uint32_t)pl.G * 2u) & 15u);
+        const uint32_t sc1 = st + (uint32_t)(P.stage_w_bytes + P.sc_half_bytes) +
+                             (((uint32_t)(row0 + pl.up_offset) * (uint32_t)pl.G * 2u) & 15u);
         const int pslot = tile % kPartSlots;
         if (tile >= kPartSlots) { /* the epilogue must have drained this partial slot */
-            if (!mbar_wait(&sm->part_empty[pslot], (uint32_t)(tile / kPartSlots - 1) & 1u, &sm->abort_flag)) {
+            if (!mbar_wait<100>(&sm->part_empty[pslot], (uint32_t)(tile / kPartSlots - 1) & 1u, &sm->abort_flag)) {
                 give_up(sm, P.sync, ST_PART_EMPTY);
                 return;
             }
         }
         float *part = sm->part[pslot];
 
-#pragma unroll
-        for (int j = 0; j < JTM; ++j) {
-            if (j >= pl.JT) break;
-            const int p = rg + j * pl.RG;
-            /* whole half-warps share (rg, j): the branch below is uniform within a half-warp */
-            if (!active || p >= rows) continue;
-            float val[NVROW];
-#pragma unroll
-            for (int i = 0; i < NVROW; ++i) val[i] = 0.0f;
+        /* all row steps of the tile first, then ONE transposed half-warp reduction of up to four
+         * values (row step x gate/up x token) instead of one reduction per row */
+        float val[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (active && !(P.debug & 1)) {
+            /* No data-dependent branches in here: a column chunk past the row end reads a clamped
+             * address against an all-zero prepared slice, a row past the tile end reads the tile's
+             * last row and its value is dropped at the store.  That leaves the compiler free to
+             * overlap the shared-memory loads and the integer chains of all chunks of a row step. */
+            const uint32_t up_bytes = (uint32_t)rows * (uint32_t)pl.rb;
+            uint32_t coff[CIT], soff[CIT];
 #pragma unroll
             for (int c = 0; c < CIT; ++c) {
-                const int col = ct + c * pl.CT;
-                if (col < pl.cpr) {
-                    const uint4 w0 = lds16(st + (size_t)p * pl.rb + (size_t)col * 16);
-                    const float s0 = bf16_bits_to_f32(sc0[p * pl.G + (col >> 2)]);
+                const int col = min(ct + c * pl.CT, pl.cpr - 1);
+                coff[c] = (uint32_t)col * 16u;
+                soff[c] = (uint32_t)(col >> 2) * 2u;
+            }
 #pragma unroll
-                    for (int m = 0; m < MT; ++m)
-                        val[m] = fmaf((float)chunk_dot(w0, xc[c][m]), s0 * xc[c][m].fac, val[m]);
-                    if (PAIRS) {
-                        const uint4 w1 = lds16(st + (size_t)(rows + p) * pl.rb + (size_t)col * 16);
-                        const float s1 = bf16_bits_to_f32(sc1[p * pl.G + (col >> 2)]);
+            for (int j = 0; j < JTM; ++j) {
+                if (j < pl.JT) { /* uniform over the CTA */
+                    const int pj = min(rg + j * pl.RG, rows - 1);
+                    const uint32_t wp = st + (uint32_t)pj * (uint32_t)pl.rb;
+                    const uint32_t s0p = sc0 + (uint32_t)pj * (uint32_t)pl.G * 2u, s1p = sc1 + (uint32_t)pj * (uint32_t)pl.G * 2u;
+                    uint4 w0[CIT], w1[CIT];
+                    float f0[CIT], f1[CIT];
 #pragma unroll
-                        for (int m = 0; m < MT; ++m)
-                            val[MT + m] = fmaf((float)chunk_dot(w1, xc[c][m]), s1 * xc[c][m].fac, val[MT + m]);
+                    for (int c = 0; c < CIT; ++c) {
+                        w0[c] = lds16_at(wp + coff[c]);
+                        f0[c] = lds_bf16_at(s0p + soff[c]);
+                        if (PAIRS) {
+                            w1[c] = lds16_at(wp + up_bytes + coff[c]);
+                            f1[c] = lds_bf16_at(s1p + soff[c]);
+                        }
+                    }
+#pragma unroll
+                    for (int c = 0; c < CIT; ++c) {
+#pragma unroll
+                        for (int m = 0; m < MT; ++m) {
+                            val[j * NVROW + m] = fmaf((float)chunk_dot(w0[c], xc[c][m]), f0[c] * xc[c][m].fac, val[j * NVROW + m]);
+                            if (PAIRS)
+                                val[j * NVROW + MT + m] = fmaf((float)chunk_dot(w1[c], xc[c][m]), f1[c] * xc[c][m].fac, val[j * NVROW + MT + m]);
+                        }
                     }
                 }
             }
-            const float r = halfwarp_reduce<NVROW>(val, lane, hmask);
+            /* whole half-warps are active or not (CT is a multiple of 16) */
+            const float r = halfwarp_reduce<4>(val, lane, hmask);
             const int l16 = lane & 15;
-            if ((l16 % (16 / NVROW)) == 0) {
-                const int vi = l16 / (16 / NVROW);
-                part[((size_t)p * NVROW + vi) * pl.nhw + (ct >> 4)] = r;
+            if ((l16 & 3) == 0) {
+                const int v = l16 >> 2, j = v / NVROW, i = v % NVROW, p = rg + j * pl.RG;
+                if (j < pl.JT && p < rows) part[((size_t)p * NVROW + i) * pl.nhw + (ct >> 4)] = r;
             }
         }
         __syncwarp();
@@ -409,7 +443,7 @@ __device__ __forceinline__ bool epilogue_phase(const FusedParams &P, const Phase
         const int tile = tile0 + lt;
         const int pslot = tile % kPartSlots;
         const int rows = min(pl.TR, row_end - (row_begin + lt * pl.TR));
-        if (!mbar_wait(&sm->part_full[pslot], (uint32_t)(tile / kPartSlots) & 1u, &sm->abort_flag)) {
+        if (!mbar_wait<100>(&sm->part_full[pslot], (uint32_t)(tile / kPartSlots) & 1u, &sm->abort_flag)) {
             give_up(sm, P.sync, ST_PART_FULL);
             return false;
         }
@@ -419,9 +453,11 @@ __device__ __forceinline__ bool epilogue_phase(const FusedParams &P, const Phase
             const int row = row_begin + lt * pl.TR + p;
             float a = 0.0f, b = 0.0f;
             const float *pa = part + ((size_t)p * NVROW + m) * pl.nhw;
+#pragma unroll 4
             for (int h = 0; h < pl.nhw; ++h) a += pa[h];
             if (PAIRS) {
                 const float *pb = part + ((size_t)p * NVROW + MT + m) * pl.nhw;
+#pragma unroll 4
                 for (int h = 0; h < pl.nhw; ++h) b += pb[h];
                 const float g = round_bf16(a), u = round_bf16(b);
                 P.act[(size_t)m * P.I + row] = f32_to_bf16_bits(silu_mul(g, u));
@@ -471,7 +507,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
     if (warp == 0) {
         /* ---------------- producer ---------------- */
         if (lane == 0) {
-            const unsigned my_gen = ld_acquire_gpu(P.sync + 1); /* grid-barrier generation at entry */
+            /* grid barrier: every CTA adds one to a monotonic counter; the launch's target is the
+             * count the previous launch left behind plus this grid's size (stable during the launch,
+             * so replaying a captured graph or changing the grid size needs no host bookkeeping) */
+            const unsigned bar_target = P.sync[1] + gridDim.x;
             stamp(P, 1);
             /* the activation vector of phase 1 */
             mbar_expect_tx(&sm->x_full[0], (uint32_t)(P.M * P.H * 2));
@@ -485,10 +524,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
             auto fetch_act = [&]() {
                 bool open = false;
                 for (uint32_t i = 0; i < kSpinLimit && !open; ++i) {
-                    open = ld_acquire_gpu(P.sync + 1) != my_gen;
+                    open = (int)(ld_acquire_gpu(P.sync + 0) - bar_target) >= 0;
                     if (!open) {
                         if ((i & 63) == 63 && sm->abort_flag) break;
-                        __nanosleep(64);
+                        __nanosleep(32);
                     }
                 }
                 if (!open) { give_up(sm, P.sync, ST_GRID_BARRIER); failed = true; return; }
@@ -503,12 +542,13 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
                  * the activation vector, so that is the moment to go and wait for the barrier; a
                  * stage holding a phase-1 tile frees up on its own. */
                 if (!act_issued && t - ns >= nt1) { fetch_act(); if (failed) break; }
-                if (t >= ns && !mbar_wait(&sm->empty[s], (uint32_t)(t / ns - 1) & 1u, &sm->abort_flag)) {
+                if (t >= ns && !mbar_wait<100>(&sm->empty[s], (uint32_t)(t / ns - 1) & 1u, &sm->abort_flag)) {
                     give_up(sm, P.sync, ST_PRODUCER_EMPTY);
                     failed = true;
                     break;
                 }
                 uint8_t *dst = ring + (size_t)s * P.stage_bytes;
+                if (P.debug & 2) { mbar_arrive(&sm->full[s]); continue; }
                 if (t < nt1) {
                     const int r0 = b1 + t * P.p1.TR, rows = min(P.p1.TR, e1 - r0);
                     const uint32_t bytes = (uint32_t)rows * P.p1.rb;
@@ -559,15 +599,10 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
         const unsigned seq = P.tp > 1 ? ld_acquire_gpu(P.sync + 2) : 0u;
         bool ok = epilogue_phase<MT, true>(P, P.p1, sm, 0, seq);
         /* arrive at the grid barrier: the act rows of this CTA are stored */
+        __threadfence(); /* every lane publishes its own act stores */
         __syncwarp();
         if (lane == 0) {
-            __threadfence();
-            const unsigned prev = atomicAdd(P.sync + 0, 1u);
-            if (prev == gridDim.x - 1) {
-                atomicExch(P.sync + 0, 0u);
-                __threadfence();
-                atomicAdd(P.sync + 1, 1u); /* release everybody */
-            }
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.sync + 0) : "memory");
             stamp(P, 5);
         }
         if (ok) ok = epilogue_phase<MT, false>(P, P.p2, sm, nt1, seq);
@@ -606,6 +641,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
     __syncthreads();
     /* the call sequence number advances once per launch (parity of the peer slots, flag target) */
     if (blockIdx.x == 0 && threadIdx.x == 0) {
+        P.sync[1] += gridDim.x; /* every CTA has arrived by now (this CTA passed the barrier) */
         if (P.tp > 1) atomicAdd(P.sync + 2, 1u);
         stamp(P, 12);
     }
@@ -672,9 +708,9 @@ static bool plan_phase(PhasePlan &pl, int K, int MT, bool pairs, int target_byte
     pl.RG = kConsumerThreads / pl.CT;
     if (pairs) {
         pl.RG = min(pl.RG, max(1, target_bytes / (2 * pl.rb)));
-        pl.JT = max(1, min(2, target_bytes / (2 * pl.RG * pl.rb)));
+        pl.JT = max(1, min(2 / MT, target_bytes / (2 * pl.RG * pl.rb)));
     } else {
-        pl.JT = max(1, min(kMaxJT, target_bytes / (pl.RG * pl.rb)));
+        pl.JT = max(1, min(kMaxJT / MT, target_bytes / (pl.RG * pl.rb)));
     }
     pl.TR = pl.JT * pl.RG;
     pl.nhw = pl.CT / 16;
@@ -738,6 +774,8 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
     P.stage_bytes = round_up(P.stage_w_bytes + 2 * P.sc_half_bytes, 128);
     P.xs_bytes = round_up(tokens * max(H, I) * 2, 128);
     P.trace = g_trace;
+    static const int debug_flags = getenv("FFN_INT4_DEBUG") ? atoi(getenv("FFN_INT4_DEBUG")) : 0;
+    P.debug = debug_flags;
     const size_t fixed = ((sizeof(Smem) + 127) / 128) * 128 + (size_t)P.xs_bytes;
     if (fixed + 2 * (size_t)P.stage_bytes > (size_t)d.smem_optin) return FFN_NOT_ADMITTED;
     P.nstages = (int)min((size_t)kMaxStages, ((size_t)d.smem_optin - fixed) / (size_t)P.stage_bytes);
