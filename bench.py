@@ -36,6 +36,9 @@ if ROOT not in sys.path:
 HIDDEN, INTER = 5120, 17408
 L2_BYTES = 126 * 1024 * 1024
 METRIC = "int4_ffn_decode_us_per_step"
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused launch at H=5120, I=17408, M=1, TP=1 (ncu --set
+# full capture summarised in profiles/ffn_fused_kernel_cfg2_tp1.md); other shapes have no capture yet.
+TRAFFIC_BYTES = {(1, 1): 142.26e6}
 
 
 def algorithmic_bytes(h, i, tp):
@@ -250,7 +253,7 @@ def run_ours(args):
                        "l2": f"rotating {copies} weight copies per rank ({copies * per_rank_bytes / 1e6:.0f} MB > 2x L2)",
                        "timing": f"{args.steps} steps in one CUDA graph, median of {reps} replays, max over ranks"},
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(gbs / peak, 4), "peak_source": peak_kind, "traffic": None,
+                         "frac": round(gbs / peak, 4), "peak_source": peak_kind, "traffic": TRAFFIC_BYTES.get((tp, m)),
                          "algorithmic_bytes_per_launch": per_rank_bytes},
             "e2e": {"value": round(e2e_us, 3), "unit": "us/step", "h2d_bytes_per_step": m * h * 2,
                     "d2h_bytes_per_step": m * h * 2},

@@ -48,7 +48,7 @@ constexpr int kConsumerThreads = kConsumerWarps * 32;  /* 544 = 17 * 32: I = 174
 constexpr int kThreads = (kConsumerWarps + 2) * 32;    /* 608 */
 constexpr int kMaxStages = 8;
 constexpr int kPartSlots = 4;
-constexpr int kPartFloats = 512;                       /* floats per partial slot */
+constexpr int kPartFloats = 160;                       /* floats per partial slot: JT*NVROW*RG*CT/16 <= 4*544/16 = 136 */
 constexpr int kMaxJT = 4;                              /* row steps per thread per tile */
 constexpr uint32_t kSpinLimit = 1u << 22;              /* bounded waits: polls of >= 32..100 ns, i.e. 0.15 .. 0.5 s */
 
@@ -76,13 +76,14 @@ struct FusedParams {
     int stage_w_bytes;    /* weights part of a stage; the tile's scales follow it */
     int sc_half_bytes;    /* room for one contiguous run of scales (gate or up) incl. 16 bytes of slack */
     unsigned *sync;       /* [0] arrivals (monotonic), [1] arrivals at the end of the previous launch,
-                             [2] call sequence, [3] status */
+                             [2] unused, [3] status */
     /* tensor parallelism (tp == 1: unused) */
     int tp, rank;
     float *const *peer_slots;   /* device array [tp]: each rank's [2][tp][M_max][H] fp32 slots */
     unsigned *const *peer_flags;/* device array [tp]: each rank's per-CTA arrival counters */
     int slot_stride;      /* floats per (parity, rank) slot = M_max * H */
-    /* optional fused residual update on the reduced output (h <- bf16(h + y)); NULL = off */
+    unsigned *tp_seq;     /* this communicator's call counter (slot parity, flag target) */
+    /* optional fused residual update with the reduced output y: h <- bf16(h + y); NULL = off */
     uint16_t *residual;
     long long *trace;     /* optional [kTraceWords] clock64 stamps of CTA 0 (NULL = off) */
     int debug;            /* measurement aid: bit 0 skips the arithmetic, bit 1 skips the weight copies */
@@ -462,12 +463,11 @@ __device__ __forceinline__ bool epilogue_phase(const FusedParams &P, const Phase
                 const float g = round_bf16(a), u = round_bf16(b);
                 P.act[(size_t)m * P.I + row] = f32_to_bf16_bits(silu_mul(g, u));
             } else if (P.tp == 1) {
-                float y = round_bf16(a);
-                if (P.residual) {
-                    y = round_bf16(bf16_bits_to_f32(P.residual[(size_t)m * P.H + row]) + y);
-                    P.residual[(size_t)m * P.H + row] = f32_to_bf16_bits(y);
-                }
+                const float y = round_bf16(a);
                 P.out[(size_t)m * P.H + row] = f32_to_bf16_bits(y);
+                if (P.residual)
+                    P.residual[(size_t)m * P.H + row] =
+                        f32_to_bf16_bits(bf16_bits_to_f32(P.residual[(size_t)m * P.H + row]) + y);
             } else {
                 const size_t off = (size_t)((seq & 1u) * P.tp + P.rank) * P.slot_stride + (size_t)m * P.H + row;
                 for (int r = 0; r < P.tp; ++r) P.peer_slots[r][off] = a; /* own slot on every rank */
@@ -596,7 +596,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
     } else {
         /* ---------------- epilogue ---------------- */
         /* read before this CTA arrives at the grid barrier: nobody can have advanced it yet */
-        const unsigned seq = P.tp > 1 ? ld_acquire_gpu(P.sync + 2) : 0u;
+        const unsigned seq = P.tp > 1 ? ld_acquire_gpu(P.tp_seq) : 0u;
         bool ok = epilogue_phase<MT, true>(P, P.p1, sm, 0, seq);
         /* arrive at the grid barrier: the act rows of this CTA are stored */
         __threadfence(); /* every lane publishes its own act stores */
@@ -627,12 +627,11 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
                     const int row = b2 + i / MT, m = i % MT;
                     float a = 0.0f;
                     for (int r = 0; r < P.tp; ++r) a += ld_relaxed_sys_f32(mine + (size_t)r * P.slot_stride + (size_t)m * P.H + row);
-                    float y = round_bf16(a);
-                    if (P.residual) {
-                        y = round_bf16(bf16_bits_to_f32(P.residual[(size_t)m * P.H + row]) + y);
-                        P.residual[(size_t)m * P.H + row] = f32_to_bf16_bits(y);
-                    }
+                    const float y = round_bf16(a);
                     P.out[(size_t)m * P.H + row] = f32_to_bf16_bits(y);
+                    if (P.residual)
+                        P.residual[(size_t)m * P.H + row] =
+                            f32_to_bf16_bits(bf16_bits_to_f32(P.residual[(size_t)m * P.H + row]) + y);
                 }
             }
             if (lane == 0) stamp(P, 11);
@@ -642,7 +641,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
     /* the call sequence number advances once per launch (parity of the peer slots, flag target) */
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         P.sync[1] += gridDim.x; /* every CTA has arrived by now (this CTA passed the barrier) */
-        if (P.tp > 1) atomicAdd(P.sync + 2, 1u);
+        if (P.tp > 1) atomicAdd(P.tp_seq, 1u);
         stamp(P, 12);
     }
 }
@@ -755,6 +754,7 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
     if (tp && tp->tp > 1) {
         P.tp = tp->tp; P.rank = tp->rank;
         P.peer_slots = tp->peer_slots; P.peer_flags = tp->peer_flags; P.slot_stride = tp->slot_stride;
+        P.tp_seq = tp->seq;
         if (tokens * H > tp->slot_stride) return fail(FFN_ERR_CONFIG, "fused FFN: %d tokens exceed the exchange buffer", tokens);
     }
     static const int target_kb = getenv("FFN_INT4_STAGE_KB") ? atoi(getenv("FFN_INT4_STAGE_KB")) : 62; /* tuning knob */

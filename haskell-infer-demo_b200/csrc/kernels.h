@@ -33,6 +33,7 @@ struct FusedTp {
     float *const *peer_slots;    /* [tp] -> each rank's [2][tp][slot_stride] fp32 */
     unsigned *const *peer_flags; /* [tp] -> each rank's per-CTA arrival counters */
     int slot_stride;             /* floats per (parity, rank) slot */
+    unsigned *seq;               /* this rank's call counter for this communicator (device word) */
     int max_ctas;                /* grid size every rank uses */
 };
 int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
