@@ -218,6 +218,22 @@ int ffn_forward_mlp_prepared(void *cublas, void *stream, const void *normed, voi
     return mlp_common((cudaStream_t)stream, normed, ws, layer_out, w, tokens, dims);
 }
 
+int ffn_forward_mlp_prepared_noalloc(void *stream, const void *normed, void *layer_out,
+                                     const FfnMlpWeights *w, int tokens, const FfnModelDims *dims) {
+    clear_error();
+    if (!dims || !w) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: null weights or dims");
+    if (!normed || !layer_out) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: null buffer");
+    if (!w->gate_up_i4 || !w->gate_up_i4_scales || !w->down_i4 || !w->down_i4_scales)
+        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: the layer carries no INT4 operands");
+    if (w->i4_group != FFN_INT4_GROUP)
+        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: this format's group is %d, not %d", FFN_INT4_GROUP, w->i4_group);
+    const int H = dims->hidden_size, I = dims->intermediate_size;
+    if (H <= 0 || I <= 0 || H % FFN_INT4_GROUP || I % FFN_INT4_GROUP)
+        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: hidden=%d / intermediate=%d are not whole numbers "
+                    "of %d-wide groups", H, I, FFN_INT4_GROUP);
+    return fused_ffn_launch_noalloc((cudaStream_t)stream, normed, layer_out, w, tokens, H, I);
+}
+
 /* ---- the reference's kernel test bridge ---------------------------------------------------- */
 
 int test_gemm_int4(void *out, const void *a, const void *packed, const void *scales, int M, int N,

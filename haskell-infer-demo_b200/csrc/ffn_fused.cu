@@ -802,6 +802,106 @@ int fused_ffn_try(cudaStream_t stream, const void *normed, void *act, void *laye
     return fused_ffn_launch(stream, normed, act, layer_out, w, tokens, H, I, nullptr, nullptr);
 }
 
+/* ------------------------------------------------------------------------------------------- */
+/* The fused FFN for callers that cannot allocate                                               */
+/* ------------------------------------------------------------------------------------------- */
+/* Some hosts give every byte of device memory to an arena of their own when they start, so a later
+ * cudaMalloc from inside a library fails; others run the decode loop in a place where the implicit
+ * device-wide synchronisation of cudaMalloc / cudaFree is not acceptable.  For them the scratch the
+ * fused kernel needs besides its inputs and outputs - the four synchronisation words and the
+ * activation vector act = SiLU(gate)*up that phase 1 hands to phase 2 through global memory - lives
+ * in this fixed array instead of in allocated memory.  Every GPU that loads the library holds these
+ * 128.25 KiB until the process exits.  Limit: tokens * intermediate_size <= kNoAllocActElems. */
+constexpr int kNoAllocActElems = 65536;                              /* bf16 elements of act */
+constexpr size_t kNoAllocSyncBytes = 256;
+constexpr size_t kNoAllocBytes = kNoAllocSyncBytes + (size_t)kNoAllocActElems * 2;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+/* Per device: the DEVICE address of the array above.  In host code the name g_noalloc_scratch is
+ * only a stand-in for the symbol; the address a kernel can use comes from cudaGetSymbolAddress,
+ * asked once per device with that device current. */
+static DeviceState g_noalloc_dev[64];
+static unsigned char *g_noalloc_ptr[64];
+
+static int noalloc_device_state(DeviceState **out, unsigned char **scratch) {
+    int dev = 0;
+    FFN_CUDA_TRY(cudaGetDevice(&dev), "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return fail(FFN_ERR_CONFIG, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DeviceState &d = g_noalloc_dev[dev];
+    if (!d.ready) {
+        FFN_CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev), "SM count");
+        FFN_CUDA_TRY(cudaDeviceGetAttribute(&d.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev), "smem opt-in");
+        FFN_CUDA_TRY(cudaDeviceGetAttribute(&d.cooperative, cudaDevAttrCooperativeLaunch, dev), "cooperative launch");
+        void *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(FFN_ERR_CUDA, "cannot resolve the static scratch array on device %d: %s", dev, cudaGetErrorString(e));
+        g_noalloc_ptr[dev] = (unsigned char *)p;
+        d.sync = (unsigned *)p; /* the first kNoAllocSyncBytes of the array */
+        d.ready = true;
+    }
+    *out = &d;
+    *scratch = g_noalloc_ptr[dev];
+    return FFN_OK;
+}
+
+int fused_ffn_launch_noalloc(cudaStream_t stream, const void *normed, void *layer_out,
+                             const FfnMlpWeights *w, int tokens, int H, int I) {
+    if (tokens < 1 || tokens > 2)
+        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: %d tokens; this entry point takes 1 or 2", tokens);
+    if ((long long)tokens * I > kNoAllocActElems)
+        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: tokens * intermediate_size = %lld exceeds the "
+                    "static scratch (%d elements)", (long long)tokens * I, kNoAllocActElems);
+    DeviceState *dp = nullptr;
+    unsigned char *scratch = nullptr;
+    const int st = noalloc_device_state(&dp, &scratch);
+    if (st) return st;
+    DeviceState &d = *dp;
+    if (!d.cooperative) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: the device cannot launch cooperatively");
+    if (((uintptr_t)w->gate_up_i4 & 15) || ((uintptr_t)w->down_i4 & 15) || ((uintptr_t)normed & 15) ||
+        ((uintptr_t)w->gate_up_i4_scales & 15) || ((uintptr_t)w->down_i4_scales & 15))
+        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: operands must be 16-byte aligned");
+
+    FusedParams P = {};
+    P.x = (const uint16_t *)normed;
+    P.act = (uint16_t *)(scratch + kNoAllocSyncBytes);
+    P.out = (uint16_t *)layer_out;
+    P.M = tokens; P.H = H; P.I = I;
+    P.sync = d.sync;
+    P.tp = 1; P.rank = 0;
+    const int target = 62 * 1024;
+    int c1 = 0, c2 = 0;
+    if (!plan_phase(P.p1, H, tokens, true, target, c1) || !plan_phase(P.p2, I, tokens, false, target, c2))
+        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: rows of %d / %d columns do not fit the kernel", H, I);
+    P.p1.w = w->gate_up_i4; P.p1.s = (const uint16_t *)w->gate_up_i4_scales;
+    P.p1.rows_total = I; P.p1.up_offset = I;
+    P.p2.w = w->down_i4; P.p2.s = (const uint16_t *)w->down_i4_scales;
+    P.p2.rows_total = H; P.p2.up_offset = 0;
+    P.stage_w_bytes = round_up(max(2 * P.p1.TR * P.p1.rb, P.p2.TR * P.p2.rb), 128);
+    P.sc_half_bytes = round_up(max(P.p1.TR * P.p1.G * 2, P.p2.TR * P.p2.G * 2) + 32, 16);
+    P.stage_bytes = round_up(P.stage_w_bytes + 2 * P.sc_half_bytes, 128);
+    P.xs_bytes = round_up(tokens * max(H, I) * 2, 128);
+    const size_t fixed = ((sizeof(Smem) + 127) / 128) * 128 + (size_t)P.xs_bytes;
+    if (P.p1.TR * 2 * tokens * P.p1.nhw > kPartFloats || P.p2.TR * tokens * P.p2.nhw > kPartFloats ||
+        fixed + 2 * (size_t)P.stage_bytes > (size_t)d.smem_optin)
+        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: the shape does not fit shared memory");
+    P.nstages = (int)min((size_t)kMaxStages, ((size_t)d.smem_optin - fixed) / (size_t)P.stage_bytes);
+    const size_t smem = fixed + (size_t)P.nstages * P.stage_bytes;
+    /* The array keeps whatever the previous call left.  The barrier words must be consistent with
+     * each other and the status word must start at zero, so they are cleared on the stream first;
+     * act needs no clearing (phase 1 writes every element phase 2 reads). */
+    FFN_CUDA_TRY(cudaMemsetAsync(d.sync, 0, 4 * sizeof(unsigned), stream), "clear the static synchronisation words");
+    const int grid = d.sm_count;
+    if (tokens == 1) {
+        if (c1 == 1 && c2 == 1) return launch_fused<1, 1, 1>(d, P, grid, smem, stream);
+        if (c1 == 1 && c2 == 2) return launch_fused<1, 2, 1>(d, P, grid, smem, stream);
+        if (c1 == 2 && c2 == 1) return launch_fused<2, 1, 1>(d, P, grid, smem, stream);
+        return launch_fused<2, 2, 1>(d, P, grid, smem, stream);
+    }
+    return launch_fused<1, 1, 2>(d, P, grid, smem, stream);
+}
+
 int fused_status(unsigned *status_out, bool reset) {
     DeviceState *dp = nullptr;
     const int st = device_state(&dp);

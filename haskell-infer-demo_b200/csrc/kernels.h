@@ -43,5 +43,8 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
  * synchronisation words so the next launch starts clean. */
 int fused_status(unsigned *status_out, bool reset);
 void fused_set_trace(long long *device_buffer);
+/* The fused FFN with its scratch in a static device array: calls no allocating routine. */
+int fused_ffn_launch_noalloc(cudaStream_t stream, const void *normed, void *layer_out,
+                             const FfnMlpWeights *w, int tokens, int H, int I);
 
 }  // namespace ffn

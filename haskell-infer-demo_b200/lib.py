@@ -56,6 +56,7 @@ def _declare(lib):
         "ffn_forward_mlp": [vp, vp, vp, vp, vp, ctypes.POINTER(MlpWeights), ci, ctypes.POINTER(ModelDims)],
         "ffn_forward_mlp_prepared": [vp, vp, vp, vp, vp, ctypes.POINTER(MlpWeights), ci,
                                      ctypes.POINTER(ModelDims)],
+        "ffn_forward_mlp_prepared_noalloc": [vp, vp, vp, ctypes.POINTER(MlpWeights), ci, ctypes.POINTER(ModelDims)],
         "ffn_tp_create": [ctypes.POINTER(vp), ci, ci, ci, ci],
         "ffn_tp_export": [vp, vp],
         "ffn_tp_connect": [vp, vp],

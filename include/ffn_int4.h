@@ -158,6 +158,24 @@ int ffn_forward_mlp_prepared(void *cublas, void *stream, const void *normed, voi
                              void *layer_out, const FfnMlpWeights *w, int tokens,
                              const FfnModelDims *dims);
 
+/* The fused FFN (as ffn_forward_mlp_prepared, 1 or 2 tokens) for callers that cannot allocate
+ * device memory: a host that handed all of the GPU's memory to its own arena at start-up, so a
+ * cudaMalloc from inside a library would fail, or a decode loop that cannot take the device-wide
+ * synchronisation cudaMalloc and cudaFree imply.  This entry point calls no cudaMalloc, cudaFree or
+ * other allocating routine and takes no workspace: the kernel's scratch (its synchronisation words
+ * and the activation vector act that phase 1 passes to phase 2) sits in a fixed 128.25 KiB array
+ * inside the library, which every GPU that loads the library holds until the process exits.
+ * Limit: tokens * dims->intermediate_size <= 65536 (e.g. one token at I = 17408, two at I <= 32768);
+ * larger requests are refused with FFN_ERR_CONFIG, as are shapes the fused kernel does not take.
+ * The first call on each device looks up the array's device address (no allocation); make that
+ * first call before any stream capture.  All calls on a device share the one array and it keeps the
+ * last call's contents: the words that must start at zero are cleared on `stream` at the start of
+ * every call, and two calls that overlap on the GPU (different streams) race - serialise them.
+ * Kernel status words of this entry point are not the ones ffn_int4_device_status reads.
+ * This entry point has no counterpart in the reference. */
+int ffn_forward_mlp_prepared_noalloc(void *stream, const void *normed, void *layer_out,
+                                     const FfnMlpWeights *w, int tokens, const FfnModelDims *dims);
+
 /* ------------------------------------------------------------------------------------------- */
 /* Tensor parallelism: the down projection's partial sums are reduced across ranks from inside    */
 /* the FFN kernel (peer stores over NVLink), replacing allreduce_sum on the layer output           */
