@@ -1,0 +1,871 @@
+/*
+ * sidecar.cu - host side of the INT4 artifact path: SHA-256, the strict reader of
+ * `weights.manifest.json`, artifact reads tied to their recorded digests, the tensor-parallel shard
+ * view and the per-rank slicing + upload of a layer's operands.
+ *
+ * Replaces, for this path: csrc/sha256.c, csrc/quant_manifest.c (quant_manifest_parse, _find_entry,
+ * _find_pair, quant_artifact_read; csrc/include/quant_manifest.h:68-147), model_desc_shard_view
+ * (csrc/model_desc.c:561-631, OUT_DIM / IN_DIM rules) and the slicing half of
+ * engine_load_quantized_ffn (csrc/engine.cu:2207-2428).  Unlike the reference's loader, which
+ * re-reads and re-hashes every artifact once per rank and uploads with blocking copies, a layer's
+ * artifacts are read and hashed once per process and the slices go up through pinned staging.
+ *
+ * The manifest functions return the reference's QuantManifestStatus values (0 OK, 1 ARG, 2 SYNTAX,
+ * 3 FORMAT, 4 SHAPE, 5 IO, 6 HASH) so the reference's refusal tests read the same against this
+ * reader; the message is in ffn_int4_last_error().
+ */
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace ffn {
+
+enum { QM_OK = 0, QM_ARG = 1, QM_SYNTAX = 2, QM_FORMAT = 3, QM_SHAPE = 4, QM_IO = 5, QM_HASH = 6 };
+
+/* ------------------------------------------------------------------------------------------- */
+/* SHA-256 (FIPS 180-4)                                                                          */
+/* ------------------------------------------------------------------------------------------- */
+static const uint32_t kSha256K[64] = {
+    0x428a2f98, 0x71374491, 0xb5c0fbcf, 0xe9b5dba5, 0x3956c25b, 0x59f111f1, 0x923f82a4, 0xab1c5ed5,
+    0xd807aa98, 0x12835b01, 0x243185be, 0x550c7dc3, 0x72be5d74, 0x80deb1fe, 0x9bdc06a7, 0xc19bf174,
+    0xe49b69c1, 0xefbe4786, 0x0fc19dc6, 0x240ca1cc, 0x2de92c6f, 0x4a7484aa, 0x5cb0a9dc, 0x76f988da,
+    0x983e5152, 0xa831c66d, 0xb00327c8, 0xbf597fc7, 0xc6e00bf3, 0xd5a79147, 0x06ca6351, 0x14292967,
+    0x27b70a85, 0x2e1b2138, 0x4d2c6dfc, 0x53380d13, 0x650a7354, 0x766a0abb, 0x81c2c92e, 0x92722c85,
+    0xa2bfe8a1, 0xa81a664b, 0xc24b8b70, 0xc76c51a3, 0xd192e819, 0xd6990624, 0xf40e3585, 0x106aa070,
+    0x19a4c116, 0x1e376c08, 0x2748774c, 0x34b0bcb5, 0x391c0cb3, 0x4ed8aa4a, 0x5b9cca4f, 0x682e6ff3,
+    0x748f82ee, 0x78a5636f, 0x84c87814, 0x8cc70208, 0x90befffa, 0xa4506ceb, 0xbef9a3f7, 0xc67178f2};
+
+struct Sha256 {
+    uint32_t h[8] = {0x6a09e667, 0xbb67ae85, 0x3c6ef372, 0xa54ff53a, 0x510e527f, 0x9b05688c, 0x1f83d9ab, 0x5be0cd19};
+    uint8_t block[64];
+    size_t fill = 0;
+    uint64_t total = 0;
+
+    static uint32_t rotr(uint32_t v, int n) { return (v >> n) | (v << (32 - n)); }
+
+    void compress(const uint8_t *p) {
+        uint32_t w[64];
+        for (int i = 0; i < 16; ++i)
+            w[i] = ((uint32_t)p[4 * i] << 24) | ((uint32_t)p[4 * i + 1] << 16) | ((uint32_t)p[4 * i + 2] << 8) | p[4 * i + 3];
+        for (int i = 16; i < 64; ++i) {
+            const uint32_t s0 = rotr(w[i - 15], 7) ^ rotr(w[i - 15], 18) ^ (w[i - 15] >> 3);
+            const uint32_t s1 = rotr(w[i - 2], 17) ^ rotr(w[i - 2], 19) ^ (w[i - 2] >> 10);
+            w[i] = w[i - 16] + s0 + w[i - 7] + s1;
+        }
+        uint32_t a = h[0], b = h[1], c = h[2], d = h[3], e = h[4], f = h[5], g = h[6], k = h[7];
+        for (int i = 0; i < 64; ++i) {
+            const uint32_t t1 = k + (rotr(e, 6) ^ rotr(e, 11) ^ rotr(e, 25)) + ((e & f) ^ (~e & g)) + kSha256K[i] + w[i];
+            const uint32_t t2 = (rotr(a, 2) ^ rotr(a, 13) ^ rotr(a, 22)) + ((a & b) ^ (a & c) ^ (b & c));
+            k = g; g = f; f = e; e = d + t1; d = c; c = b; b = a; a = t1 + t2;
+        }
+        h[0] += a; h[1] += b; h[2] += c; h[3] += d; h[4] += e; h[5] += f; h[6] += g; h[7] += k;
+    }
+    void update(const uint8_t *p, size_t n) {
+        total += n;
+        if (fill) {
+            const size_t take = n < 64 - fill ? n : 64 - fill;
+            memcpy(block + fill, p, take);
+            fill += take; p += take; n -= take;
+            if (fill == 64) { compress(block); fill = 0; }
+        }
+        for (; n >= 64; p += 64, n -= 64) compress(p);
+        if (n) { memcpy(block, p, n); fill = n; }
+    }
+    void finish(char hex[65]) {
+        const uint64_t bits = total * 8;
+        const uint8_t one = 0x80, zero = 0;
+        update(&one, 1);
+        while (fill != 56) update(&zero, 1);
+        uint8_t len[8];
+        for (int i = 0; i < 8; ++i) len[i] = (uint8_t)(bits >> (56 - 8 * i));
+        update(len, 8);
+        static const char *digits = "0123456789abcdef";
+        for (int i = 0; i < 8; ++i)
+            for (int j = 0; j < 4; ++j) {
+                const uint8_t byte = (uint8_t)(h[i] >> (24 - 8 * j));
+                hex[8 * i + 2 * j] = digits[byte >> 4];
+                hex[8 * i + 2 * j + 1] = digits[byte & 15];
+            }
+        hex[64] = '\0';
+    }
+};
+
+/* ------------------------------------------------------------------------------------------- */
+/* A small strict JSON reader (objects refuse duplicate keys; nothing may follow the document)   */
+/* ------------------------------------------------------------------------------------------- */
+struct Json {
+    enum Kind { Null, Bool, Int, Real, Str, Arr, Obj } kind = Null;
+    long long i = 0;
+    double d = 0;
+    bool b = false;
+    std::string s;
+    std::vector<Json> a;
+    std::vector<std::pair<std::string, Json>> o;
+    const Json *get(const char *key) const {
+        for (const auto &kv : o)
+            if (kv.first == key) return &kv.second;
+        return nullptr;
+    }
+};
+
+struct JsonReader {
+    const char *p, *end;
+    std::string error;
+    int depth = 0;
+    explicit JsonReader(const char *text) : p(text), end(text + strlen(text)) {}
+    void ws() { while (p < end && (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r')) ++p; }
+    bool fail_at(const char *what) { if (error.empty()) error = std::string("quant manifest: ") + what; return false; }
+    bool string(std::string &out) {
+        if (p >= end || *p != '"') return fail_at("a string was expected");
+        ++p;
+        out.clear();
+        while (p < end && *p != '"') {
+            unsigned char c = (unsigned char)*p++;
+            if (c < 0x20) return fail_at("a control character inside a string");
+            if (c == '\\') {
+                if (p >= end) return fail_at("the document ends inside a string");
+                const char e = *p++;
+                switch (e) {
+                case '"': out += '"'; break; case '\\': out += '\\'; break; case '/': out += '/'; break;
+                case 'b': out += '\b'; break; case 'f': out += '\f'; break; case 'n': out += '\n'; break;
+                case 'r': out += '\r'; break; case 't': out += '\t'; break;
+                case 'u': {
+                    if (end - p < 4) return fail_at("a truncated \\u escape");
+                    unsigned v = 0;
+                    for (int k = 0; k < 4; ++k) {
+                        const char h = *p++;
+                        v <<= 4;
+                        if (h >= '0' && h <= '9') v |= (unsigned)(h - '0');
+                        else if (h >= 'a' && h <= 'f') v |= (unsigned)(h - 'a' + 10);
+                        else if (h >= 'A' && h <= 'F') v |= (unsigned)(h - 'A' + 10);
+                        else return fail_at("a malformed \\u escape");
+                    }
+                    if (v < 0x80) out += (char)v;
+                    else if (v < 0x800) { out += (char)(0xC0 | (v >> 6)); out += (char)(0x80 | (v & 0x3F)); }
+                    else { out += (char)(0xE0 | (v >> 12)); out += (char)(0x80 | ((v >> 6) & 0x3F)); out += (char)(0x80 | (v & 0x3F)); }
+                    break;
+                }
+                default: return fail_at("an unknown escape");
+                }
+            } else {
+                out += (char)c;
+            }
+        }
+        if (p >= end) return fail_at("the document ends inside a string");
+        ++p;
+        return true;
+    }
+    bool value(Json &out) {
+        if (++depth > 32) return fail_at("nesting too deep");
+        ws();
+        if (p >= end) return fail_at("the document is truncated");
+        bool ok = true;
+        if (*p == '{') {
+            out.kind = Json::Obj;
+            ++p; ws();
+            if (p < end && *p == '}') { ++p; }
+            else {
+                for (;;) {
+                    ws();
+                    std::string key;
+                    if (!string(key)) { ok = false; break; }
+                    if (out.get(key.c_str())) { ok = fail_at(("the key \"" + key + "\" appears twice").c_str()); break; }
+                    ws();
+                    if (p >= end || *p != ':') { ok = fail_at("':' was expected"); break; }
+                    ++p;
+                    out.o.emplace_back(key, Json());
+                    if (!value(out.o.back().second)) { ok = false; break; }
+                    ws();
+                    if (p < end && *p == ',') { ++p; continue; }
+                    if (p < end && *p == '}') { ++p; break; }
+                    ok = fail_at("',' or '}' was expected (the document is truncated or malformed)");
+                    break;
+                }
+            }
+        } else if (*p == '[') {
+            out.kind = Json::Arr;
+            ++p; ws();
+            if (p < end && *p == ']') { ++p; }
+            else {
+                for (;;) {
+                    out.a.emplace_back();
+                    if (!value(out.a.back())) { ok = false; break; }
+                    ws();
+                    if (p < end && *p == ',') { ++p; continue; }
+                    if (p < end && *p == ']') { ++p; break; }
+                    ok = fail_at("',' or ']' was expected (the document is truncated or malformed)");
+                    break;
+                }
+            }
+        } else if (*p == '"') {
+            out.kind = Json::Str;
+            ok = string(out.s);
+        } else if (!strncmp(p, "true", 4)) { out.kind = Json::Bool; out.b = true; p += 4; }
+        else if (!strncmp(p, "false", 5)) { out.kind = Json::Bool; out.b = false; p += 5; }
+        else if (!strncmp(p, "null", 4)) { out.kind = Json::Null; p += 4; }
+        else {
+            const char *start = p;
+            if (p < end && *p == '-') ++p;
+            bool digits = false, real = false;
+            while (p < end && *p >= '0' && *p <= '9') { ++p; digits = true; }
+            if (p < end && *p == '.') { real = true; ++p; while (p < end && *p >= '0' && *p <= '9') ++p; }
+            if (p < end && (*p == 'e' || *p == 'E')) {
+                real = true; ++p;
+                if (p < end && (*p == '+' || *p == '-')) ++p;
+                while (p < end && *p >= '0' && *p <= '9') ++p;
+            }
+            if (!digits) ok = fail_at("a value was expected");
+            else {
+                const std::string text(start, p);
+                if (real) { out.kind = Json::Real; out.d = strtod(text.c_str(), nullptr); }
+                else {
+                    if (text.size() > 18) ok = fail_at("an integer is out of range");
+                    out.kind = Json::Int; out.i = strtoll(text.c_str(), nullptr, 10); out.d = (double)out.i;
+                }
+            }
+        }
+        --depth;
+        return ok;
+    }
+};
+
+}  // namespace ffn
+
+/* ------------------------------------------------------------------------------------------- */
+/* The manifest                                                                                  */
+/* ------------------------------------------------------------------------------------------- */
+namespace ffn {
+
+struct Artifact {
+    std::string file, dtype, sha256;
+    long long bytes = -1, count = -1;
+};
+struct Entry {
+    std::string role;
+    int role_index = -1, layer = -1;
+    long long n = 0, k = 0, group = 0;
+    Artifact packed, scales;
+};
+struct Pair {
+    std::string name, member_role[2];
+    int member_role_index[2] = {-1, -1};
+    int layer = -1;
+    long long n = 0, k = 0, group = 0;
+    Artifact packed, scales;
+};
+struct Manifest {
+    int manifest_version = 0, format_abi_version = 0, qmin = 0, qmax = 0, zero_point = 0, invalid_code = 0;
+    long long group = 0;
+    std::string packed_dtype, scale_dtype, converter_name, source_model_dir;
+    int converter_version = 0;
+    std::vector<Entry> entries;
+    std::vector<Pair> pairs;
+    int int4_cells = 0, bf16_cells = 0;
+};
+
+constexpr int kMaxEntries = 256, kMaxPairs = 128; /* csrc/include/quant_manifest.h:47-51 */
+
+static int qfail(int status, const char *fmt, ...) {
+    char buf[480];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    fail(status, "%s", buf);
+    return status;
+}
+
+static bool as_int(const Json *j, long long *out) {
+    if (!j || j->kind != Json::Int) return false;
+    *out = j->i;
+    return true;
+}
+static bool as_str(const Json *j, std::string *out) {
+    if (!j || j->kind != Json::Str) return false;
+    *out = j->s;
+    return true;
+}
+
+static bool is_sha256_hex(const std::string &s) {
+    if (s.size() != 64) return false;
+    for (char c : s)
+        if (!((c >= '0' && c <= '9') || (c >= 'a' && c <= 'f'))) return false;
+    return true;
+}
+
+/* One artifact object.  `is_scales` artifacts carry a count; packed ones do not. */
+static int read_artifact(const Json *j, Artifact *a, const char *want_dtype, const char *where, bool is_scales) {
+    if (!j || j->kind != Json::Obj) return qfail(QM_SYNTAX, "quant manifest: %s has no %s artifact", where, is_scales ? "scales" : "packed");
+    long long bytes = -1, count = -1;
+    if (!as_str(j->get("file"), &a->file) || a->file.empty() || !as_str(j->get("dtype"), &a->dtype) ||
+        !as_str(j->get("sha256"), &a->sha256) || !as_int(j->get("bytes"), &bytes))
+        return qfail(QM_SYNTAX, "quant manifest: %s has an incomplete %s artifact", where, is_scales ? "scales" : "packed");
+    if (is_scales && !as_int(j->get("count"), &count))
+        return qfail(QM_SYNTAX, "quant manifest: %s's scales record no count", where);
+    a->bytes = bytes;
+    a->count = is_scales ? count : -1;
+    if (a->dtype != want_dtype)
+        return qfail(QM_FORMAT, "quant manifest: %s's %s artifact is %s, the format stores %s", where,
+                     is_scales ? "scales" : "packed", a->dtype.c_str(), want_dtype);
+    if (!is_sha256_hex(a->sha256))
+        return qfail(QM_FORMAT, "quant manifest: %s's %s digest is not 64 lower-case hex digits", where,
+                     is_scales ? "scales" : "packed");
+    if (a->bytes < 0 || (is_scales && a->count < 0))
+        return qfail(QM_SHAPE, "quant manifest: %s records a negative extent", where);
+    if (a->file.size() >= 512 || a->file[0] == '/' || a->file.find("..") != std::string::npos)
+        return qfail(QM_FORMAT, "quant manifest: %s names an artifact outside the sidecar directory", where);
+    return QM_OK;
+}
+
+/* The format's extent rules (linear_layout_init, csrc/linear_weight.cpp:57-86). */
+static int layout_of(long long n, long long k, long long group, long long *packed_bytes, long long *scale_count, const char *where) {
+    if (n <= 0 || k <= 0) return qfail(QM_SHAPE, "quant manifest: %s has a nonpositive shape", where);
+    if (group != FFN_INT4_GROUP) return qfail(QM_SHAPE, "quant manifest: %s groups %lld, this format's group is %d", where, group, FFN_INT4_GROUP);
+    if (k % group) return qfail(QM_SHAPE, "quant manifest: %s: K=%lld is not a whole number of %lld-wide groups", where, k, group);
+    if (n % 8) return qfail(QM_SHAPE, "quant manifest: %s: N=%lld is not a whole number of the 8-row tile", where, n);
+    *packed_bytes = n * k / 2;
+    *scale_count = n * (k / group);
+    return QM_OK;
+}
+
+static int read_shape(const Json *j, long long *n, long long *k) {
+    if (!j || j->kind != Json::Arr || j->a.size() != 2 || j->a[0].kind != Json::Int || j->a[1].kind != Json::Int) return 0;
+    *n = j->a[0].i;
+    *k = j->a[1].i;
+    return 1;
+}
+
+static int find_entry(const Manifest &m, int layer, const char *role) {
+    for (size_t i = 0; i < m.entries.size(); ++i)
+        if (m.entries[i].layer == layer && m.entries[i].role == role) return (int)i;
+    return -1;
+}
+static int find_pair(const Manifest &m, const char *name, int layer) {
+    for (size_t i = 0; i < m.pairs.size(); ++i)
+        if (m.pairs[i].layer == layer && m.pairs[i].name == name) return (int)i;
+    return -1;
+}
+
+static int parse_manifest(const char *text, Manifest *m) {
+    if (!text || !m) return qfail(QM_ARG, "quant manifest: null argument");
+    JsonReader reader(text);
+    Json root;
+    reader.ws();
+    if (reader.p >= reader.end) return qfail(QM_SYNTAX, "quant manifest: the document is empty");
+    if (!reader.value(root)) return qfail(QM_SYNTAX, "%s", reader.error.c_str());
+    reader.ws();
+    if (reader.p != reader.end) return qfail(QM_SYNTAX, "quant manifest: bytes follow the document");
+    if (root.kind != Json::Obj) return qfail(QM_SYNTAX, "quant manifest: the document is not an object");
+    const Json *format = root.get("format"), *entries = root.get("entries"), *pairs = root.get("pairs"),
+               *precision = root.get("precision_map"), *converter = root.get("converter"), *source = root.get("source");
+    long long version = 0;
+    if (!as_int(root.get("manifest_version"), &version) || !format || format->kind != Json::Obj || !entries ||
+        entries->kind != Json::Arr || !pairs || pairs->kind != Json::Arr || !precision || precision->kind != Json::Arr)
+        return qfail(QM_SYNTAX, "quant manifest: a required section (manifest_version, format, entries, pairs, precision_map) is missing");
+    if (version != 1) return qfail(QM_FORMAT, "quant manifest: manifest_version %lld, this reader speaks 1", version);
+    m->manifest_version = (int)version;
+
+    /* the format block has to be the frozen format (csrc/include/linear_weight.h:46-54) */
+    long long abi = 0, group = 0, qmin = 0, qmax = 0, zp = 0, invalid = 0;
+    if (!as_int(format->get("abi_version"), &abi) || !as_int(format->get("group"), &group) || !as_int(format->get("qmin"), &qmin) ||
+        !as_int(format->get("qmax"), &qmax) || !as_int(format->get("zero_point"), &zp) || !as_int(format->get("invalid_code"), &invalid) ||
+        !as_str(format->get("packed_dtype"), &m->packed_dtype) || !as_str(format->get("scale_dtype"), &m->scale_dtype))
+        return qfail(QM_SYNTAX, "quant manifest: the format block is incomplete");
+    if (abi != 1) return qfail(QM_FORMAT, "quant manifest: format abi_version %lld, this reader speaks 1", abi);
+    if (group != FFN_INT4_GROUP || qmin != -7 || qmax != 7 || zp != 0 || invalid != -8)
+        return qfail(QM_FORMAT, "quant manifest: the format block (group %lld, codes [%lld, %lld], zero point %lld, reserved %lld) "
+                     "is not the frozen format", group, qmin, qmax, zp, invalid);
+    if (m->packed_dtype != "u8" || m->scale_dtype != "bf16")
+        return qfail(QM_FORMAT, "quant manifest: the format stores %s codes and %s scales, not u8 and bf16",
+                     m->packed_dtype.c_str(), m->scale_dtype.c_str());
+    m->format_abi_version = (int)abi; m->group = group; m->qmin = (int)qmin; m->qmax = (int)qmax;
+    m->zero_point = (int)zp; m->invalid_code = (int)invalid;
+    if (converter && converter->kind == Json::Obj) {
+        long long cv = 0;
+        as_str(converter->get("name"), &m->converter_name);
+        if (as_int(converter->get("version"), &cv)) m->converter_version = (int)cv;
+    }
+    if (source && source->kind == Json::Obj) as_str(source->get("model_dir"), &m->source_model_dir);
+
+    if (entries->a.size() > (size_t)kMaxEntries) return qfail(QM_SHAPE, "quant manifest: more than %d entries", kMaxEntries);
+    for (const Json &e : entries->a) {
+        if (e.kind != Json::Obj) return qfail(QM_SYNTAX, "quant manifest: an entry is not an object");
+        Entry en;
+        long long layer = -1, role_index = -1, group_e = 0;
+        std::string axis;
+        if (!as_str(e.get("role"), &en.role) || !as_int(e.get("layer"), &layer) || !as_int(e.get("group"), &group_e) ||
+            !read_shape(e.get("logical_shape"), &en.n, &en.k))
+            return qfail(QM_SYNTAX, "quant manifest: an entry lacks role, layer, group or logical_shape");
+        if (en.role.empty() || en.role.size() >= 64) return qfail(QM_FORMAT, "quant manifest: an entry has no usable role");
+        if (layer < 0) return qfail(QM_FORMAT, "quant manifest: %s has a negative layer", en.role.c_str());
+        if (as_str(e.get("group_axis"), &axis) && axis != "k")
+            return qfail(QM_FORMAT, "quant manifest: %s groups along %s, the format groups along k", en.role.c_str(), axis.c_str());
+        as_int(e.get("role_index"), &role_index);
+        en.layer = (int)layer; en.role_index = (int)role_index; en.group = group_e;
+        char where[128];
+        snprintf(where, sizeof(where), "%s layer %d", en.role.c_str(), en.layer);
+        long long pb = 0, sc = 0;
+        int st = layout_of(en.n, en.k, en.group, &pb, &sc, where);
+        if (st) return st;
+        if ((st = read_artifact(e.get("packed"), &en.packed, "u8", where, false))) return st;
+        if ((st = read_artifact(e.get("scales"), &en.scales, "bf16", where, true))) return st;
+        if (en.packed.bytes != pb)
+            return qfail(QM_SHAPE, "quant manifest: %s records %lld packed bytes, [%lld, %lld] at group %lld is %lld", where,
+                         en.packed.bytes, en.n, en.k, en.group, pb);
+        if (en.scales.count != sc)
+            return qfail(QM_SHAPE, "quant manifest: %s records %lld scales, [%lld, %lld] at group %lld is %lld", where,
+                         en.scales.count, en.n, en.k, en.group, sc);
+        if (en.scales.bytes != en.scales.count * 2)
+            return qfail(QM_SHAPE, "quant manifest: %s records %lld scale bytes for %lld bf16 scales", where, en.scales.bytes, en.scales.count);
+        if (find_entry(*m, en.layer, en.role.c_str()) >= 0) return qfail(QM_SHAPE, "quant manifest: %s appears twice", where);
+        m->entries.push_back(en);
+    }
+
+    if (pairs->a.size() > (size_t)kMaxPairs) return qfail(QM_SHAPE, "quant manifest: more than %d pairs", kMaxPairs);
+    for (const Json &pj : pairs->a) {
+        if (pj.kind != Json::Obj) return qfail(QM_SYNTAX, "quant manifest: a pair is not an object");
+        Pair pr;
+        long long layer = -1;
+        const Json *members = pj.get("members");
+        if (!as_str(pj.get("name"), &pr.name) || !as_int(pj.get("layer"), &layer) || !as_int(pj.get("group"), &pr.group) ||
+            !read_shape(pj.get("logical_shape"), &pr.n, &pr.k) || !members || members->kind != Json::Arr || members->a.size() != 2)
+            return qfail(QM_SYNTAX, "quant manifest: a pair lacks name, layer, group, logical_shape or its two members");
+        pr.layer = (int)layer;
+        char where[160];
+        snprintf(where, sizeof(where), "pair %s layer %d", pr.name.c_str(), pr.layer);
+        int st;
+        if ((st = read_artifact(pj.get("packed"), &pr.packed, "u8", where, false))) return st;
+        if ((st = read_artifact(pj.get("scales"), &pr.scales, "bf16", where, true))) return st;
+        if (pr.n <= 0 || pr.k <= 0) return qfail(QM_SHAPE, "quant manifest: %s has a nonpositive shape", where);
+        long long rows = 0, pbytes = 0, scales = 0, k = -1;
+        for (int i = 0; i < 2; ++i) {
+            const Json &mj = members->a[i];
+            long long ri = -1;
+            if (mj.kind != Json::Obj || !as_str(mj.get("role"), &pr.member_role[i]))
+                return qfail(QM_SYNTAX, "quant manifest: %s has a member without a role", where);
+            if (as_int(mj.get("role_index"), &ri)) pr.member_role_index[i] = (int)ri;
+            const int idx = find_entry(*m, pr.layer, pr.member_role[i].c_str());
+            if (idx < 0)
+                return qfail(QM_SHAPE, "quant manifest: %s names member %s, which is not an entry of layer %d", where,
+                             pr.member_role[i].c_str(), pr.layer);
+            const Entry &en = m->entries[idx];
+            if (pr.member_role_index[i] >= 0 && pr.member_role_index[i] != en.role_index)
+                return qfail(QM_SHAPE, "quant manifest: %s records member %s as role_index %d, the entry is %d", where,
+                             en.role.c_str(), pr.member_role_index[i], en.role_index);
+            if (k < 0) k = en.k;
+            else if (en.k != k) return qfail(QM_SHAPE, "quant manifest: %s concatenates members of different K (%lld and %lld)", where, k, en.k);
+            rows += en.n; pbytes += en.packed.bytes; scales += en.scales.count;
+        }
+        if (pr.k != k || pr.n != rows)
+            return qfail(QM_SHAPE, "quant manifest: %s is [%lld, %lld], its members are [%lld, %lld]", where, pr.n, pr.k, rows, k);
+        if (pr.packed.bytes != pbytes) return qfail(QM_SHAPE, "quant manifest: %s records %lld packed bytes, its members hold %lld", where, pr.packed.bytes, pbytes);
+        if (pr.scales.count != scales || pr.scales.bytes != scales * 2)
+            return qfail(QM_SHAPE, "quant manifest: %s records %lld scales, its members hold %lld", where, pr.scales.count, scales);
+        if (pr.group != FFN_INT4_GROUP) return qfail(QM_FORMAT, "quant manifest: %s groups %lld, the format groups %d", where, pr.group, FFN_INT4_GROUP);
+        m->pairs.push_back(pr);
+    }
+
+    /* the precision map and the entries have to describe the same cells */
+    std::vector<char> seen(m->entries.size(), 0);
+    for (const Json &c : precision->a) {
+        std::string role, prec;
+        long long layer = -1;
+        if (c.kind != Json::Obj || !as_str(c.get("role"), &role) || !as_str(c.get("precision"), &prec) || !as_int(c.get("layer"), &layer))
+            return qfail(QM_SYNTAX, "quant manifest: a precision cell lacks role, layer or precision");
+        if (prec == "int4") {
+            const int idx = find_entry(*m, (int)layer, role.c_str());
+            if (idx < 0) return qfail(QM_SHAPE, "quant manifest: %s layer %lld is marked int4 but has no entry", role.c_str(), layer);
+            if (seen[idx]) return qfail(QM_SHAPE, "quant manifest: %s layer %lld has two precision cells", role.c_str(), layer);
+            seen[idx] = 1;
+            ++m->int4_cells;
+        } else if (prec == "bf16") {
+            if (find_entry(*m, (int)layer, role.c_str()) >= 0)
+                return qfail(QM_SHAPE, "quant manifest: %s layer %lld has an entry but is marked bf16", role.c_str(), layer);
+            ++m->bf16_cells;
+        } else {
+            return qfail(QM_FORMAT, "quant manifest: unknown precision %s", prec.c_str());
+        }
+    }
+    for (size_t i = 0; i < seen.size(); ++i)
+        if (!seen[i])
+            return qfail(QM_SHAPE, "quant manifest: %s layer %d has an entry but no int4 precision cell", m->entries[i].role.c_str(), m->entries[i].layer);
+    return QM_OK;
+}
+
+/* Read one artifact, checking size, dtype and SHA-256 in that order (quant_artifact_read,
+ * csrc/quant_manifest.c:1085-1139). */
+static int read_artifact_file(const std::string &root, const Artifact &a, const char *want_dtype, std::vector<uint8_t> *out) {
+    if (a.dtype != want_dtype)
+        return qfail(QM_FORMAT, "quant artifact %s is recorded as %s, %s was expected", a.file.c_str(), a.dtype.c_str(), want_dtype);
+    const std::string path = root + "/" + a.file;
+    FILE *f = fopen(path.c_str(), "rb");
+    if (!f) return qfail(QM_IO, "quant artifact %s cannot be opened", path.c_str());
+    fseek(f, 0, SEEK_END);
+    const long long size = ftell(f);
+    fseek(f, 0, SEEK_SET);
+    if (size != a.bytes) {
+        fclose(f);
+        return qfail(QM_IO, "quant artifact %s is %lld bytes, the manifest records %lld", path.c_str(), size, a.bytes);
+    }
+    out->resize((size_t)size);
+    const size_t got = size ? fread(out->data(), 1, (size_t)size, f) : 0;
+    fclose(f);
+    if ((long long)got != size) return qfail(QM_IO, "quant artifact %s could not be read in full", path.c_str());
+    Sha256 sha;
+    sha.update(out->data(), out->size());
+    char hex[65];
+    sha.finish(hex);
+    if (a.sha256 != hex) {
+        out->clear();
+        return qfail(QM_HASH, "quant artifact %s hashes to %s, the manifest records %s", path.c_str(), hex, a.sha256.c_str());
+    }
+    return QM_OK;
+}
+
+}  // namespace ffn
+
+/* ------------------------------------------------------------------------------------------- */
+/* Shard views and the per-rank load                                                             */
+/* ------------------------------------------------------------------------------------------- */
+namespace ffn {
+
+enum { SHARD_NONE = 0, SHARD_OUT_DIM = 1, SHARD_IN_DIM = 2 };
+
+/* model_desc_shard_view's OUT_DIM / IN_DIM rules (csrc/model_desc.c:609-626). */
+static int shard_view(int rule, long long rows, long long cols, int tp, int rank, long long v[4]) {
+    v[0] = 0; v[1] = rows; v[2] = 0; v[3] = cols;
+    if (tp <= 1) return FFN_OK;
+    if (rank < 0 || rank >= tp) return fail(FFN_ERR_CONFIG, "shard view rank %d is outside [0, %d)", rank, tp);
+    if (rule == SHARD_OUT_DIM) {
+        if (rows % tp) return fail(FFN_ERR_CONFIG, "tp_size %d does not divide %lld rows", tp, rows);
+        v[1] = rows / tp; v[0] = v[1] * rank;
+    } else if (rule == SHARD_IN_DIM) {
+        if (cols % tp) return fail(FFN_ERR_CONFIG, "tp_size %d does not divide %lld columns", tp, cols);
+        v[3] = cols / tp; v[2] = v[3] * rank;
+    } else if (rule != SHARD_NONE) {
+        return fail(FFN_ERR_CONFIG, "unknown shard rule %d", rule);
+    }
+    return FFN_OK;
+}
+
+struct LoadedLayer {
+    uint8_t *gate_up = nullptr, *down = nullptr;
+    uint16_t *gate_up_scales = nullptr, *down_scales = nullptr;
+};
+struct QuantizedFfn {
+    int device = 0, layers = 0, hidden = 0, inter_local = 0;
+    std::vector<LoadedLayer> layer;
+    std::vector<void *> owned;
+    ~QuantizedFfn() {
+        int restore = 0;
+        (void)cudaGetDevice(&restore);
+        (void)cudaSetDevice(device);
+        for (void *p : owned) cudaFree(p);
+        (void)cudaSetDevice(restore);
+    }
+};
+
+/* `rows` rows of `row_bytes` starting at (first_row, col_byte) of a row-major source whose rows are
+ * `src_row_bytes` wide.  Payload and scales use the same walk with their own widths, so the scales
+ * copied are the global ones the slice selects (slice_rows, csrc/engine.cu:2198-2205). */
+static void slice_into(uint8_t *dst, const uint8_t *src, long long src_row_bytes, long long first_row, long long rows,
+                       long long col_byte, long long row_bytes) {
+    for (long long i = 0; i < rows; ++i)
+        memcpy(dst + i * row_bytes, src + (first_row + i) * src_row_bytes + col_byte, (size_t)row_bytes);
+}
+
+struct Staging { /* pinned, double-buffered by layer parity */
+    uint8_t *buf[2] = {nullptr, nullptr};
+    size_t bytes = 0;
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    ~Staging() {
+        for (int i = 0; i < 2; ++i) {
+            if (buf[i]) cudaFreeHost(buf[i]);
+            if (done[i]) cudaEventDestroy(done[i]);
+        }
+    }
+};
+
+static int load_ranks(const char *dir, int num_layers, int hidden, int inter, int tp, const int *ranks, const int *devices,
+                      int count, QuantizedFfn **out) {
+    if (!dir || !out || !ranks || !devices || count < 1) return fail(FFN_ERR_CONFIG, "ffn_load_quantized_ffn: null argument");
+    if (num_layers < 1) return fail(FFN_ERR_CONFIG, "ffn_load_quantized_ffn: this descriptor has no dense FFN layer to quantize");
+    const std::string root(dir);
+    std::string text;
+    {
+        FILE *f = fopen((root + "/weights.manifest.json").c_str(), "rb");
+        if (!f) return fail(FFN_ERR_WEIGHTS, "ffn_load_quantized_ffn: cannot open %s/weights.manifest.json", dir);
+        char chunk[8192];
+        size_t got;
+        while ((got = fread(chunk, 1, sizeof(chunk), f)) > 0) text.append(chunk, got);
+        fclose(f);
+    }
+    Manifest m;
+    if (parse_manifest(text.c_str(), &m) != QM_OK) {
+        const std::string why = ffn_int4_last_error();
+        return fail(FFN_ERR_WEIGHTS, "ffn_load_quantized_ffn: %s", why.c_str());
+    }
+    /* every dense layer or none (csrc/engine.cu:2245-2262) */
+    int prepared = 0;
+    for (int l = 0; l < num_layers; ++l)
+        if (find_pair(m, "mlpGateUp", l) >= 0 && find_entry(m, l, "mlpDown") >= 0) ++prepared;
+    if (prepared != num_layers)
+        return fail(FFN_ERR_WEIGHTS, "ffn_load_quantized_ffn: the sidecar covers %d of %d dense layers", prepared, num_layers);
+
+    std::vector<std::unique_ptr<QuantizedFfn>> result;
+    for (int i = 0; i < count; ++i) {
+        std::unique_ptr<QuantizedFfn> q(new QuantizedFfn());
+        q->device = devices[i]; q->layers = num_layers; q->hidden = hidden; q->inter_local = inter / (tp > 0 ? tp : 1);
+        q->layer.resize(num_layers);
+        result.push_back(std::move(q));
+    }
+    std::vector<Staging> staging(count);
+    std::vector<cudaStream_t> streams(count, nullptr);
+    int restore = 0;
+    (void)cudaGetDevice(&restore);
+    int status = FFN_OK;
+    auto upload = [&](int i, int parity, size_t *offset, const std::vector<uint8_t> &host, void **dev_out) -> int {
+        QuantizedFfn &q = *result[i];
+        void *d = nullptr;
+        if (cudaMalloc(&d, host.size() ? host.size() : 16) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return fail(FFN_ERR_ALLOC, "ffn_load_quantized_ffn: cannot allocate %zu bytes on device %d", host.size(), q.device);
+        }
+        q.owned.push_back(d);
+        memcpy(staging[i].buf[parity] + *offset, host.data(), host.size());
+        FFN_CUDA_TRY(cudaMemcpyAsync(d, staging[i].buf[parity] + *offset, host.size(), cudaMemcpyHostToDevice, streams[i]),
+                     "ffn_load_quantized_ffn: upload");
+        *offset += (host.size() + 255) & ~(size_t)255;
+        *dev_out = d;
+        return FFN_OK;
+    };
+
+    for (int l = 0; l < num_layers && status == FFN_OK; ++l) {
+        const Pair &pair = m.pairs[find_pair(m, "mlpGateUp", l)];
+        const Entry &down = m.entries[find_entry(m, l, "mlpDown")];
+        if (pair.n != 2ll * inter || pair.k != hidden) {
+            status = fail(FFN_ERR_WEIGHTS, "ffn_load_quantized_ffn: layer %d's mlpGateUp pair is [%lld, %lld], the checkpoint's gate+up is [%lld, %d]",
+                          l, pair.n, pair.k, 2ll * inter, hidden);
+            break;
+        }
+        if (down.n != hidden || down.k != inter) {
+            status = fail(FFN_ERR_WEIGHTS, "ffn_load_quantized_ffn: layer %d's mlpDown is [%lld, %lld], the checkpoint's is [%d, %d]", l,
+                          down.n, down.k, hidden, inter);
+            break;
+        }
+        if (pair.group != down.group) {
+            status = fail(FFN_ERR_WEIGHTS, "ffn_load_quantized_ffn: layer %d's gate/up and down disagree on the group width", l);
+            break;
+        }
+        /* read and hash each artifact ONCE, whatever the number of ranks */
+        std::vector<uint8_t> pair_p, pair_s, down_p, down_s;
+        if (read_artifact_file(root, pair.packed, "u8", &pair_p) || read_artifact_file(root, pair.scales, "bf16", &pair_s) ||
+            read_artifact_file(root, down.packed, "u8", &down_p) || read_artifact_file(root, down.scales, "bf16", &down_s)) {
+            const std::string why = ffn_int4_last_error();
+            status = fail(FFN_ERR_WEIGHTS, "ffn_load_quantized_ffn: %s", why.c_str());
+            break;
+        }
+        const long long half_rows = pair.n / 2;
+        for (int i = 0; i < count && status == FFN_OK; ++i) {
+            const int r = ranks[i];
+            long long gv[4], dv[4];
+            if ((status = shard_view(SHARD_OUT_DIM, half_rows, pair.k, tp, r, gv)) != FFN_OK) break;
+            if ((status = shard_view(SHARD_IN_DIM, down.n, down.k, tp, r, dv)) != FFN_OK) break;
+            if (gv[2] % pair.group || dv[2] % down.group || dv[3] % down.group) {
+                status = fail(FFN_ERR_WEIGHTS, "ffn_load_quantized_ffn: layer %d's rank %d splits K at a non-group boundary, which cannot "
+                              "retain the global scales", l, r);
+                break;
+            }
+            const long long row_b = gv[3] / 2, srow_b = gv[3] / pair.group * 2;
+            std::vector<uint8_t> gu_p((size_t)(2 * gv[1] * row_b)), gu_s((size_t)(2 * gv[1] * srow_b));
+            slice_into(gu_p.data(), pair_p.data(), pair.k / 2, gv[0], gv[1], gv[2] / 2, row_b);
+            slice_into(gu_p.data() + gv[1] * row_b, pair_p.data(), pair.k / 2, half_rows + gv[0], gv[1], gv[2] / 2, row_b);
+            slice_into(gu_s.data(), pair_s.data(), pair.k / pair.group * 2, gv[0], gv[1], gv[2] / pair.group * 2, srow_b);
+            slice_into(gu_s.data() + gv[1] * srow_b, pair_s.data(), pair.k / pair.group * 2, half_rows + gv[0], gv[1],
+                       gv[2] / pair.group * 2, srow_b);
+            const long long drow_b = dv[3] / 2, dsrow_b = dv[3] / down.group * 2;
+            std::vector<uint8_t> d_p((size_t)(down.n * drow_b)), d_s((size_t)(down.n * dsrow_b));
+            slice_into(d_p.data(), down_p.data(), down.k / 2, 0, down.n, dv[2] / 2, drow_b);
+            slice_into(d_s.data(), down_s.data(), down.k / down.group * 2, 0, down.n, dv[2] / down.group * 2, dsrow_b);
+
+            if (cudaSetDevice(devices[i]) != cudaSuccess) { status = fail(FFN_ERR_CUDA, "ffn_load_quantized_ffn: cannot select device %d", devices[i]); break; }
+            Staging &st = staging[i];
+            const size_t need = gu_p.size() + gu_s.size() + d_p.size() + d_s.size() + 4 * 256;
+            if (!st.buf[0]) {
+                st.bytes = need;
+                if (cudaMallocHost(&st.buf[0], need) != cudaSuccess || cudaMallocHost(&st.buf[1], need) != cudaSuccess ||
+                    cudaEventCreateWithFlags(&st.done[0], cudaEventDisableTiming) != cudaSuccess ||
+                    cudaEventCreateWithFlags(&st.done[1], cudaEventDisableTiming) != cudaSuccess ||
+                    cudaStreamCreateWithFlags(&streams[i], cudaStreamNonBlocking) != cudaSuccess) {
+                    status = fail(FFN_ERR_ALLOC, "ffn_load_quantized_ffn: cannot set up pinned staging");
+                    break;
+                }
+            }
+            const int parity = l & 1;
+            if (l >= 2 && cudaEventSynchronize(st.done[parity]) != cudaSuccess) { status = fail(FFN_ERR_CUDA, "ffn_load_quantized_ffn: staging wait"); break; }
+            size_t off = 0;
+            LoadedLayer &ll = result[i]->layer[l];
+            if ((status = upload(i, parity, &off, gu_p, (void **)&ll.gate_up)) || (status = upload(i, parity, &off, gu_s, (void **)&ll.gate_up_scales)) ||
+                (status = upload(i, parity, &off, d_p, (void **)&ll.down)) || (status = upload(i, parity, &off, d_s, (void **)&ll.down_scales)))
+                break;
+            (void)cudaEventRecord(st.done[parity], streams[i]);
+        }
+    }
+    for (int i = 0; i < count; ++i)
+        if (streams[i]) {
+            (void)cudaSetDevice(devices[i]);
+            if (cudaStreamSynchronize(streams[i]) != cudaSuccess && status == FFN_OK) status = fail(FFN_ERR_CUDA, "ffn_load_quantized_ffn: upload failed");
+            cudaStreamDestroy(streams[i]);
+        }
+    (void)cudaSetDevice(restore);
+    if (status != FFN_OK) return status; /* unique_ptrs free what was uploaded: all or nothing */
+    for (int i = 0; i < count; ++i) out[i] = result[i].release();
+    return FFN_OK;
+}
+
+}  // namespace ffn
+
+using namespace ffn;
+
+extern "C" {
+
+struct FfnQuantManifest { Manifest m; };
+
+int ffn_sha256_hex(const void *data, size_t len, char *out65) {
+    if ((!data && len) || !out65) return FFN_ERR_CONFIG;
+    Sha256 sha;
+    sha.update((const uint8_t *)data, len);
+    sha.finish(out65);
+    return FFN_OK;
+}
+
+int ffn_quant_manifest_parse(const char *json, FfnQuantManifest **out) {
+    clear_error();
+    if (!json || !out) return qfail(QM_ARG, "quant manifest: null argument");
+    std::unique_ptr<FfnQuantManifest> h(new FfnQuantManifest());
+    const int st = parse_manifest(json, &h->m);
+    if (st != QM_OK) return st;
+    *out = h.release();
+    return QM_OK;
+}
+
+void ffn_quant_manifest_free(FfnQuantManifest *m) { delete m; }
+
+int ffn_quant_manifest_counts(const FfnQuantManifest *m, int *entries, int *pairs, int *int4_cells, int *bf16_cells) {
+    if (!m) return QM_ARG;
+    if (entries) *entries = (int)m->m.entries.size();
+    if (pairs) *pairs = (int)m->m.pairs.size();
+    if (int4_cells) *int4_cells = m->m.int4_cells;
+    if (bf16_cells) *bf16_cells = m->m.bf16_cells;
+    return QM_OK;
+}
+
+int ffn_quant_manifest_find_entry(const FfnQuantManifest *m, int layer, const char *role) {
+    return (m && role) ? find_entry(m->m, layer, role) : -1;
+}
+
+int ffn_quant_manifest_find_pair(const FfnQuantManifest *m, const char *name, int layer) {
+    return (m && name) ? find_pair(m->m, name, layer) : -1;
+}
+
+int ffn_quant_manifest_entry_shape(const FfnQuantManifest *m, int index, long long *n, long long *k, long long *group, int *role_index) {
+    if (!m || index < 0 || index >= (int)m->m.entries.size()) return QM_ARG;
+    const Entry &e = m->m.entries[index];
+    if (n) *n = e.n;
+    if (k) *k = e.k;
+    if (group) *group = e.group;
+    if (role_index) *role_index = e.role_index;
+    return QM_OK;
+}
+
+int ffn_quant_manifest_pair_shape(const FfnQuantManifest *m, int index, long long *n, long long *k, long long *group) {
+    if (!m || index < 0 || index >= (int)m->m.pairs.size()) return QM_ARG;
+    const Pair &p = m->m.pairs[index];
+    if (n) *n = p.n;
+    if (k) *k = p.k;
+    if (group) *group = p.group;
+    return QM_OK;
+}
+
+int ffn_quant_artifact_read(const char *root, const char *file, const char *dtype, long long bytes, const char *sha256,
+                            const char *want_dtype, uint8_t **out, size_t *out_len) {
+    clear_error();
+    if (!root || !file || !dtype || !sha256 || !want_dtype || !out || !out_len) return qfail(QM_ARG, "quant artifact: null argument");
+    *out = nullptr;
+    *out_len = 0;
+    Artifact a;
+    a.file = file; a.dtype = dtype; a.bytes = bytes; a.sha256 = sha256;
+    std::vector<uint8_t> data;
+    const int st = read_artifact_file(root, a, want_dtype, &data);
+    if (st != QM_OK) return st;
+    uint8_t *buf = (uint8_t *)malloc(data.size() ? data.size() : 1);
+    if (!buf) return qfail(QM_IO, "quant artifact: out of memory");
+    memcpy(buf, data.data(), data.size());
+    *out = buf;
+    *out_len = data.size();
+    return QM_OK;
+}
+
+void ffn_host_free(void *p) { free(p); }
+
+int ffn_shard_view(int rule, long long rows, long long cols, int tp, int rank, long long *view4) {
+    clear_error();
+    if (!view4) return fail(FFN_ERR_CONFIG, "ffn_shard_view: null argument");
+    return shard_view(rule, rows, cols, tp, rank, view4);
+}
+
+int ffn_load_quantized_ffn(const char *manifest_dir, int num_layers, int hidden, int intermediate, int tp, int rank,
+                           FfnQuantizedFfn **out) {
+    clear_error();
+    if (!out) return fail(FFN_ERR_CONFIG, "ffn_load_quantized_ffn: null argument");
+    int dev = 0;
+    FFN_CUDA_TRY(cudaGetDevice(&dev), "ffn_load_quantized_ffn: no CUDA device");
+    QuantizedFfn *q = nullptr;
+    const int st = load_ranks(manifest_dir, num_layers, hidden, intermediate, tp < 1 ? 1 : tp, &rank, &dev, 1, &q);
+    if (st == FFN_OK) *out = (FfnQuantizedFfn *)q;
+    return st;
+}
+
+int ffn_load_quantized_ffn_ranks(const char *manifest_dir, int num_layers, int hidden, int intermediate, int tp,
+                                 const int *devices, FfnQuantizedFfn **out) {
+    clear_error();
+    if (!out || !devices || tp < 1 || tp > 16) return fail(FFN_ERR_CONFIG, "ffn_load_quantized_ffn_ranks: bad arguments");
+    int ranks[16];
+    QuantizedFfn *q[16] = {};
+    for (int i = 0; i < tp; ++i) ranks[i] = i;
+    const int st = load_ranks(manifest_dir, num_layers, hidden, intermediate, tp, ranks, devices, tp, q);
+    if (st == FFN_OK)
+        for (int i = 0; i < tp; ++i) out[i] = (FfnQuantizedFfn *)q[i];
+    return st;
+}
+
+int ffn_quantized_ffn_layer(const FfnQuantizedFfn *handle, int layer, FfnMlpWeights *w) {
+    clear_error();
+    const QuantizedFfn *q = (const QuantizedFfn *)handle;
+    if (!q || !w) return fail(FFN_ERR_CONFIG, "ffn_quantized_ffn_layer: null argument");
+    if (layer < 0 || layer >= q->layers) return fail(FFN_ERR_CONFIG, "ffn_quantized_ffn_layer: layer %d is outside [0, %d)", layer, q->layers);
+    const LoadedLayer &l = q->layer[layer];
+    w->gate_up_i4 = l.gate_up;
+    w->gate_up_i4_scales = l.gate_up_scales;
+    w->down_i4 = l.down;
+    w->down_i4_scales = l.down_scales;
+    w->i4_group = FFN_INT4_GROUP;
+    return FFN_OK;
+}
+
+int ffn_quantized_ffn_free(FfnQuantizedFfn *handle) {
+    delete (QuantizedFfn *)handle;
+    return FFN_OK;
+}
+
+}  // extern "C"

@@ -63,10 +63,29 @@ def _declare(lib):
         "ffn_tp_connect_local": [ctypes.POINTER(vp), ci],
         "ffn_tp_destroy": [vp],
         "ffn_forward_mlp_tp": [vp, vp, vp, vp, vp, ctypes.POINTER(MlpWeights), ci, ctypes.POINTER(ModelDims), vp],
+        "ffn_sha256_hex": [vp, ctypes.c_size_t, vp],
+        "ffn_quant_manifest_parse": [ctypes.c_char_p, ctypes.POINTER(vp)],
+        "ffn_quant_manifest_counts": [vp] + [ctypes.POINTER(ci)] * 4,
+        "ffn_quant_manifest_find_entry": [vp, ci, ctypes.c_char_p],
+        "ffn_quant_manifest_find_pair": [vp, ctypes.c_char_p, ci],
+        "ffn_quant_manifest_entry_shape": [vp, ci] + [ctypes.POINTER(ctypes.c_longlong)] * 3 + [ctypes.POINTER(ci)],
+        "ffn_quant_manifest_pair_shape": [vp, ci] + [ctypes.POINTER(ctypes.c_longlong)] * 3,
+        "ffn_quant_artifact_read": [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_longlong,
+                                    ctypes.c_char_p, ctypes.c_char_p, ctypes.POINTER(vp),
+                                    ctypes.POINTER(ctypes.c_size_t)],
+        "ffn_shard_view": [ci, ctypes.c_longlong, ctypes.c_longlong, ci, ci, ctypes.POINTER(ctypes.c_longlong)],
+        "ffn_load_quantized_ffn": [ctypes.c_char_p, ci, ci, ci, ci, ci, ctypes.POINTER(vp)],
+        "ffn_load_quantized_ffn_ranks": [ctypes.c_char_p, ci, ci, ci, ci, ctypes.POINTER(ci), ctypes.POINTER(vp)],
+        "ffn_quantized_ffn_layer": [vp, ci, ctypes.POINTER(MlpWeights)],
+        "ffn_quantized_ffn_free": [vp],
         "test_gemm_int4": [vp, vp, vp, vp, ci, ci, ci, ci],
         "test_silu_mul_packed": [vp, vp, ci, ci],
         "test_norm": [vp, vp, vp, ci, ci],
     }
+    lib.ffn_quant_manifest_free.argtypes = [vp]
+    lib.ffn_quant_manifest_free.restype = None
+    lib.ffn_host_free.argtypes = [vp]
+    lib.ffn_host_free.restype = None
     lib.ffn_int4_debug_trace.argtypes = [vp]
     lib.ffn_int4_debug_trace.restype = None
     for name, args in sigs.items():

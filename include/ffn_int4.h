@@ -211,6 +211,65 @@ int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *
                        const FfnMlpWeights *w, int tokens, const FfnModelDims *dims, void *residual);
 
 /* ------------------------------------------------------------------------------------------- */
+/* The artifact path: sidecar manifest, digests, shard views, per-rank load                        */
+/* ------------------------------------------------------------------------------------------- */
+
+/* Replaces sha256_hex (csrc/include/sha256.h; csrc/sha256.c): lower-case hex digest, NUL-terminated. */
+int ffn_sha256_hex(const void *data, size_t len, char *out65);
+
+/* Replaces quant_manifest_parse and its lookups (csrc/include/quant_manifest.h:121-137;
+ * csrc/quant_manifest.c:895-1083).  These functions return the reference's QuantManifestStatus
+ * values: 0 OK, 1 ARG, 2 SYNTAX, 3 FORMAT, 4 SHAPE, 5 IO, 6 HASH (quant_manifest.h:53-61); the
+ * message is in ffn_int4_last_error().  Same schema and refusals: version 1, the frozen format block,
+ * per entry packed.bytes == N*K/2, scales.count == N*K/128, scales.bytes == 2*count, dtypes u8/bf16,
+ * 64 lower-case hex digests, a pair is its members' rows in order, the precision map and the entries
+ * describe the same cells, duplicate keys / truncation / trailing bytes refused, at most 256 entries
+ * and 128 pairs. */
+typedef struct FfnQuantManifest FfnQuantManifest;
+int ffn_quant_manifest_parse(const char *json, FfnQuantManifest **out);
+void ffn_quant_manifest_free(FfnQuantManifest *manifest);
+int ffn_quant_manifest_counts(const FfnQuantManifest *manifest, int *entries, int *pairs, int *int4_cells,
+                              int *bf16_cells);
+int ffn_quant_manifest_find_entry(const FfnQuantManifest *manifest, int layer, const char *role); /* index or -1 */
+int ffn_quant_manifest_find_pair(const FfnQuantManifest *manifest, const char *name, int layer);  /* index or -1 */
+int ffn_quant_manifest_entry_shape(const FfnQuantManifest *manifest, int index, long long *n, long long *k,
+                                   long long *group, int *role_index);
+int ffn_quant_manifest_pair_shape(const FfnQuantManifest *manifest, int index, long long *n, long long *k,
+                                  long long *group);
+
+/* Replaces quant_artifact_read (quant_manifest.h:139-143; csrc/quant_manifest.c:1085-1139): reads
+ * root/file, requiring the recorded size, then the expected dtype, then the SHA-256, in that order.
+ * On success *out is a malloc'd buffer the caller releases with ffn_host_free; on refusal *out is NULL. */
+int ffn_quant_artifact_read(const char *root, const char *file, const char *dtype, long long bytes,
+                            const char *sha256, const char *want_dtype, uint8_t **out, size_t *out_len);
+void ffn_host_free(void *p);
+
+/* Replaces model_desc_shard_view for the two rules this path uses (csrc/model_desc.c:561-631):
+ * rule 0 = none, 1 = OUT_DIM (rows split), 2 = IN_DIM (columns split).  view4 = {row_off, rows,
+ * col_off, cols}.  Uneven splits and out-of-range ranks are refused (FFN_ERR_CONFIG). */
+int ffn_shard_view(int rule, long long rows, long long cols, int tp, int rank, long long *view4);
+
+/* Replaces the INT4 half of engine_load_quantized_ffn (csrc/include/engine.h:98;
+ * csrc/engine.cu:2207-2428) for `num_layers` dense layers of shape hidden x intermediate (the whole,
+ * unsliced intermediate size): reads manifest_dir/weights.manifest.json, requires an mlpGateUp pair
+ * [2I, H] and an mlpDown entry [H, I] for every layer (all or nothing), verifies every artifact's size,
+ * dtype and SHA-256 once, keeps rank `rank` of `tp`'s slice - gate rows and up rows
+ * [rank*I/tp, (rank+1)*I/tp), down columns likewise, with the global scales those slices select;
+ * a split that lands inside a 128-group is refused with "splits K at a non-group boundary" - and
+ * uploads it to the current device through pinned staging.  FFN_ERR_WEIGHTS on any refusal. */
+typedef struct FfnQuantizedFfn FfnQuantizedFfn;
+int ffn_load_quantized_ffn(const char *manifest_dir, int num_layers, int hidden, int intermediate, int tp,
+                           int rank, FfnQuantizedFfn **out);
+/* The same for a process that drives every rank (the reference's model): reads and hashes each
+ * artifact once and slices it for all `tp` ranks; out[r] lives on devices[r]. */
+int ffn_load_quantized_ffn_ranks(const char *manifest_dir, int num_layers, int hidden, int intermediate,
+                                 int tp, const int *devices, FfnQuantizedFfn **out);
+/* Fills the INT4 members of `w` (gate_up_i4, its scales, down_i4, its scales, i4_group) with the
+ * layer's device pointers, which stay owned by the handle (LayerWeights::owned, csrc/engine.cu:2184). */
+int ffn_quantized_ffn_layer(const FfnQuantizedFfn *handle, int layer, FfnMlpWeights *w);
+int ffn_quantized_ffn_free(FfnQuantizedFfn *handle);
+
+/* ------------------------------------------------------------------------------------------- */
 /* The reference's kernel test bridge (tests/kernels/kernel_bridge.cu), same names and           */
 /* signatures, so the reference's own gate scripts can be pointed at this library.  Synchronous. */
 /* Every pointer may be a host pointer or a device pointer; host buffers are staged.            */
