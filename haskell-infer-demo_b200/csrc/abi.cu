@@ -53,6 +53,20 @@ static int mlp_common(cudaStream_t stream, const void *normed, void *ws, void *l
     uint16_t *act = packed_act + (size_t)2 * tokens * I;         /* [T, I] */
     int st = g_fused_enabled ? fused_ffn_try(stream, normed, act, layer_out, w, tokens, H, I) : FFN_NOT_ADMITTED;
     if (st != FFN_NOT_ADMITTED) return st;
+    if (g_fused_enabled) { /* 3..64 tokens per pass on the tensor cores; longer batches in blocks of 64 */
+        unsigned *status = nullptr;
+        if ((st = fused_status_word(&status))) return st;
+        bool taken = true;
+        for (int m0 = 0; m0 < tokens && taken; m0 += 64) {
+            const int m = tokens - m0 < 64 ? tokens - m0 : 64;
+            st = mma_ffn_launch(stream, (const uint16_t *)normed + (size_t)m0 * H, act + (size_t)m0 * I,
+                                (uint16_t *)layer_out + (size_t)m0 * H, w, m, H, I, nullptr, nullptr, status);
+            if (st == FFN_NOT_ADMITTED) { taken = false; break; }
+            if (st) return st;
+        }
+        if (taken) return FFN_OK;
+        if (tokens > 64) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp: the batched kernel does not take this shape");
+    }
     st = gemm_int4_generic(normed, w->gate_up_i4, w->gate_up_i4_scales, packed_act, nullptr, tokens,
                            2 * I, H, stream);
     if (st) return st;

@@ -902,6 +902,14 @@ int fused_ffn_launch_noalloc(cudaStream_t stream, const void *normed, void *laye
     return launch_fused<1, 1, 2>(d, P, grid, smem, stream);
 }
 
+int fused_status_word(unsigned **out) {
+    DeviceState *dp = nullptr;
+    const int st = device_state(&dp);
+    if (st) return st;
+    *out = dp->sync + 3;
+    return FFN_OK;
+}
+
 int fused_status(unsigned *status_out, bool reset) {
     DeviceState *dp = nullptr;
     const int st = device_state(&dp);

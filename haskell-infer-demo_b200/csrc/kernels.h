@@ -43,6 +43,11 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
  * synchronisation words so the next launch starts clean. */
 int fused_status(unsigned *status_out, bool reset);
 void fused_set_trace(long long *device_buffer);
+/* ffn_mma.cu: the tensor-core path for 3..64 tokens (two launches: gate/up + SiLU*up, down + reduce). */
+int mma_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
+                   const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual, unsigned *status);
+/* Device address of the status word shared by the kernels of this library (allocating it on first use). */
+int fused_status_word(unsigned **out);
 /* The fused FFN with its scratch in a static device array: calls no allocating routine. */
 int fused_ffn_launch_noalloc(cudaStream_t stream, const void *normed, void *layer_out,
                              const FfnMlpWeights *w, int tokens, int H, int I);

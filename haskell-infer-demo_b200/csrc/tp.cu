@@ -175,7 +175,7 @@ int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *
     if (!c || !w || !dims || !normed || !ws || !layer_out) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: null argument");
     if (!c->connected) return fail(FFN_ERR_STATE, "ffn_forward_mlp_tp: the communicator is not connected");
     if (dims->hidden_size != c->hidden) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: hidden size %d, communicator built for %d", dims->hidden_size, c->hidden);
-    if (tokens < 1 || tokens > c->max_tokens) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: %d tokens, communicator built for at most %d", tokens, c->max_tokens);
+    if (tokens < 1 || tokens > c->max_tokens || tokens > 64) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: %d tokens, communicator built for at most %d", tokens, c->max_tokens);
     if (!w->gate_up_i4 || !w->gate_up_i4_scales || !w->down_i4 || !w->down_i4_scales || w->i4_group != FFN_INT4_GROUP)
         return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: the layer carries no INT4 operands");
     const int H = dims->hidden_size, I = dims->intermediate_size;
@@ -187,7 +187,12 @@ int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *
     t.seq = (unsigned *)(c->local + 1024);
     t.max_ctas = kTpMaxCtas;
     uint16_t *act = (uint16_t *)ws + (size_t)tokens * H + (size_t)2 * tokens * I;
-    const int st = fused_ffn_launch((cudaStream_t)stream, normed, act, layer_out, w, tokens, H, I, &t, residual);
+    int st = fused_ffn_launch((cudaStream_t)stream, normed, act, layer_out, w, tokens, H, I, &t, residual);
+    if (st == FFN_NOT_ADMITTED && tokens <= 64) {
+        unsigned *status = nullptr;
+        if ((st = fused_status_word(&status))) return st;
+        st = mma_ffn_launch((cudaStream_t)stream, normed, act, layer_out, w, tokens, H, I, &t, residual, status);
+    }
     if (st == FFN_NOT_ADMITTED)
         return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: the fused kernel does not take this shape (tokens=%d H=%d I=%d)", tokens, H, I);
     return st;

@@ -37,7 +37,7 @@ def test_tp_parity_multi_gpu(ranks):
         pytest.skip(f"needs {ranks} GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}",
            "--master-addr", "127.0.0.1", "--master-port", str(29530 + ranks),
-           os.path.join(ROOT, "tests", "tp_worker.py"), "0:1", "0:2", "1:1"]
+           os.path.join(ROOT, "tests", "tp_worker.py"), "0:1", "0:2", "0:8", "0:16", "1:1", "1:64"]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
     assert proc.returncode == 0 and "tp_worker ok" in proc.stdout, proc.stdout[-3000:] + proc.stderr[-3000:]

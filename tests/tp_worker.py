@@ -44,7 +44,7 @@ def main():
         want = o.ffn(layers[0], x)
         mlp = upload_layer(layers[0], dev, tp=world, rank=rank)
         if h not in comms:
-            comms[h] = TpComm.over_process_group(h, 2)
+            comms[h] = TpComm.over_process_group(h, 64)
         comm = comms[h]
         xd = dev_bf16(x, dev)
         got_t = comm.forward_mlp(mlp, xd)
@@ -62,7 +62,7 @@ def main():
         L.device_status()
         assert torch.equal(again.view(torch.int16), got_t.view(torch.int16))
         # fused residual update: h <- bf16(h + y)
-        hres = o.bf16_round(np.random.default_rng(5).standard_normal((tokens, h), dtype=np.float32))
+        hres = o.bf16_round(np.random.default_rng(5).standard_normal((tokens, h), dtype=np.float32))  # residual stream
         res = dev_bf16(hres, dev)
         y = comm.forward_mlp(mlp, xd, residual=res)
         L.device_status()
