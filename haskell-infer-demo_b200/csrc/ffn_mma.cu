@@ -103,17 +103,37 @@ __device__ __forceinline__ void mma_block(const MmaParams &P, int row0, uint8_t 
     auto row_of = [&](int r) -> int { /* global weight row of local row r */
         return PAIRS ? (r < 16 ? row0 + r : P.up_offset + row0 + (r - 16)) : row0 + r;
     };
+    /* Each thread copies the same pieces of every chunk: 4 weight pieces (row r = i/16, 16-byte column
+     * c = i%16) and NT*4 activation pieces (token m = i/64, column c = i%64).  Sources and shared
+     * offsets are fixed per thread, so a chunk costs one add per piece. */
+    const uint8_t *wsrc[4];
+    uint32_t wdst[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int i = tid + q * kMmaThreads, r = i >> 4, c = i & 15;
+        wsrc[q] = P.w + (size_t)row_of(r) * (P.K / 2) + c * 16;
+        wdst[q] = (uint32_t)(r * kWRowBytes + c * 16);
+    }
+    const uint16_t *xsrc[NT * 4];
+    uint32_t xdst[NT * 4];
+#pragma unroll
+    for (int q = 0; q < NT * 4; ++q) {
+        const int i = tid + q * kMmaThreads, m = i >> 6, c = i & 63;
+        xsrc[q] = m < P.M ? P.x + (size_t)m * P.K + c * 8 : nullptr;
+        xdst[q] = (uint32_t)(kMmaRows * kWRowBytes + m * xrow + c * 16);
+    }
+    const int tcol_w = (tid & 15) * 32, tcol_x = (tid & 63) * 8; /* first K index of this thread's pieces */
     auto issue = [&](int chunk) {
         const uint32_t st = sbase + (uint32_t)(chunk % stages) * stage_bytes;
         const int k0 = chunk * kMmaKC, kc = min(kMmaKC, P.K - k0);
-        for (int i = tid; i < kMmaRows * (kc / 32); i += kMmaThreads) { /* 16-byte pieces of weight rows */
-            const int r = i / (kc / 32), c = i % (kc / 32);
-            cp_async16(st + r * kWRowBytes + c * 16, P.w + (size_t)row_of(r) * (P.K / 2) + k0 / 2 + c * 16);
+        if (tcol_w < kc) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) cp_async16(st + wdst[q], wsrc[q] + k0 / 2);
         }
-        const uint32_t xs = st + kMmaRows * kWRowBytes;
-        for (int i = tid; i < NT * 8 * (kc / 8); i += kMmaThreads) {
-            const int m = i / (kc / 8), c = i % (kc / 8);
-            if (m < P.M) cp_async16(xs + m * xrow + c * 16, P.x + (size_t)m * P.K + k0 + c * 8);
+        if (tcol_x < kc) {
+#pragma unroll
+            for (int q = 0; q < NT * 4; ++q)
+                if (xsrc[q]) cp_async16(st + xdst[q], xsrc[q] + k0);
         }
         cp_async_commit();
     };
