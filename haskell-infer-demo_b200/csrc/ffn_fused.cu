@@ -85,6 +85,11 @@ struct FusedParams {
     unsigned *tp_seq;     /* this communicator's call counter (slot parity, flag target) */
     /* optional fused residual update with the reduced output y: h <- bf16(h + y); NULL = off */
     uint16_t *residual;
+    /* optional fused RMSNorm of the input (x is then the residual stream h): n = bf16(h * rsqrt(mean(h^2)
+     * + eps) * (w + gemma)); NULL = x is already normalized */
+    const uint16_t *norm_w;
+    float norm_eps;
+    int norm_gemma;
     long long *trace;     /* optional [kTraceWords] clock64 stamps of CTA 0 (NULL = off) */
     int debug;            /* measurement aid: bit 0 skips the arithmetic, bit 1 skips the weight copies */
 };
@@ -198,13 +203,28 @@ struct XChunk {
     float fac;
 };
 
-__device__ __forceinline__ void prepare_chunk(XChunk &xc, const uint16_t *src /* shared, 64-byte aligned */, bool on) {
+__device__ __forceinline__ void prepare_chunk(XChunk &xc, const uint16_t *src /* shared, 64-byte aligned */, bool on,
+                                              const uint16_t *norm_w = nullptr /* global, this chunk's 32 weights */,
+                                              float inv_rms = 1.0f, float gemma = 0.0f) {
     uint32_t v[16];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         uint4 t = make_uint4(0, 0, 0, 0);
         if (on) t = lds16(src + q * 8);
         v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+    }
+    if (norm_w != nullptr && on) { /* fused RMSNorm: the reference's expression and its BF16 rounding */
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint4 wq = __ldg((const uint4 *)(norm_w + q * 8));
+            const uint32_t ww[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float lo = bf16_lo(v[4 * q + i]) * inv_rms * (bf16_lo(ww[i]) + gemma);
+                const float hi = bf16_hi(v[4 * q + i]) * inv_rms * (bf16_hi(ww[i]) + gemma);
+                v[4 * q + i] = (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
+            }
+        }
     }
     uint32_t mx = 0; /* per-halfword maximum of the magnitude bits */
 #pragma unroll
@@ -297,6 +317,7 @@ struct Smem {
     uint64_t x_full[2];
     int abort_flag;
     int pad[11];
+    float norm_red[2][kConsumerWarps + 3];
     float part[kPartSlots][kPartFloats];
 };
 
@@ -335,13 +356,42 @@ __device__ __forceinline__ void consume_phase(const FusedParams &P, const PhaseP
         give_up(sm, P.sync, ST_X_FULL);
         return;
     }
+    float inv_rms[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) inv_rms[m] = 1.0f;
+    const bool normalize = PAIRS && P.norm_w != nullptr;
+    if (normalize) { /* every CTA needs the whole normalized vector, so every CTA takes the (cheap) norm */
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float ss = 0.0f;
+            const uint32_t *row = (const uint32_t *)(xs + (size_t)m * pl.K);
+            for (int i = ti; i < pl.K / 2; i += kConsumerThreads) {
+                const uint32_t pr = row[i];
+                ss = fmaf(bf16_lo(pr), bf16_lo(pr), ss);
+                ss = fmaf(bf16_hi(pr), bf16_hi(pr), ss);
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) sm->norm_red[m][ti >> 5] = ss;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float total = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) total += sm->norm_red[m][w];
+            inv_rms[m] = rsqrtf(total / (float)pl.K + P.norm_eps);
+        }
+    }
     XChunk xc[CIT][MT];
 #pragma unroll
     for (int c = 0; c < CIT; ++c)
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             const int col = ct + c * pl.CT;
-            prepare_chunk(xc[c][m], xs + (size_t)m * pl.K + (size_t)col * 32, active && col < pl.cpr);
+            const bool on = active && col < pl.cpr;
+            prepare_chunk(xc[c][m], xs + (size_t)m * pl.K + (size_t)col * 32, on,
+                          normalize ? P.norm_w + (size_t)min(col, pl.cpr - 1) * 32 : nullptr, inv_rms[m],
+                          P.norm_gemma ? 1.0f : 0.0f);
         }
     if (threadIdx.x == 32) stamp(P, PAIRS ? 2 : 7);
 
@@ -732,7 +782,8 @@ static int launch_fused(DeviceState &d, const FusedParams &P, int grid, size_t s
 }
 
 int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
-                     const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual) {
+                     const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual,
+                     const FusedNorm *norm) {
     if (tokens < 1 || tokens > 2) return FFN_NOT_ADMITTED;
     DeviceState *dp = nullptr;
     const int st = device_state(&dp);
@@ -751,6 +802,10 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
     P.sync = d.sync;
     P.tp = 1; P.rank = 0;
     P.residual = (uint16_t *)residual;
+    if (norm && norm->weight) {
+        if ((uintptr_t)norm->weight & 15) return FFN_NOT_ADMITTED;
+        P.norm_w = (const uint16_t *)norm->weight; P.norm_eps = norm->eps; P.norm_gemma = norm->gemma;
+    }
     if (tp && tp->tp > 1) {
         P.tp = tp->tp; P.rank = tp->rank;
         P.peer_slots = tp->peer_slots; P.peer_flags = tp->peer_flags; P.slot_stride = tp->slot_stride;
@@ -799,7 +854,7 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
 
 int fused_ffn_try(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                   const FfnMlpWeights *w, int tokens, int H, int I) {
-    return fused_ffn_launch(stream, normed, act, layer_out, w, tokens, H, I, nullptr, nullptr);
+    return fused_ffn_launch(stream, normed, act, layer_out, w, tokens, H, I, nullptr, nullptr, nullptr);
 }
 
 /* ------------------------------------------------------------------------------------------- */

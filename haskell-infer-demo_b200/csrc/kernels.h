@@ -36,8 +36,15 @@ struct FusedTp {
     unsigned *seq;               /* this rank's call counter for this communicator (device word) */
     int max_ctas;                /* grid size every rank uses */
 };
+/* Optional RMSNorm fused into the kernel's input stage (weight == NULL: the input is already normalized). */
+struct FusedNorm {
+    const void *weight; /* bf16 [H] */
+    float eps;
+    int gemma;          /* 1: scale by (1 + w), 0: by w */
+};
 int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
-                     const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual);
+                     const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual,
+                     const FusedNorm *norm);
 /* Reads (synchronously) the status word the fused kernel writes when a bounded wait runs out:
  * 0 = fine, else (where | cta << 8).  With reset, a non-zero status also clears the kernel's
  * synchronisation words so the next launch starts clean. */

@@ -187,7 +187,7 @@ int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *
     t.seq = (unsigned *)(c->local + 1024);
     t.max_ctas = kTpMaxCtas;
     uint16_t *act = (uint16_t *)ws + (size_t)tokens * H + (size_t)2 * tokens * I;
-    int st = fused_ffn_launch((cudaStream_t)stream, normed, act, layer_out, w, tokens, H, I, &t, residual);
+    int st = fused_ffn_launch((cudaStream_t)stream, normed, act, layer_out, w, tokens, H, I, &t, residual, nullptr);
     if (st == FFN_NOT_ADMITTED && tokens <= 64) {
         unsigned *status = nullptr;
         if ((st = fused_status_word(&status))) return st;
@@ -196,6 +196,59 @@ int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *
     if (st == FFN_NOT_ADMITTED)
         return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: the fused kernel does not take this shape (tokens=%d H=%d I=%d)", tokens, H, I);
     return st;
+}
+
+
+/* One layer of the decode stack: h <- bf16(h + FFN(RMSNorm(h))) */
+static int decode_layer(TpComm *c, cudaStream_t stream, void *h, void *ws, void *layer_out, const FfnMlpWeights *w,
+                        int tokens, const FfnModelDims *dims) {
+    const int H = dims->hidden_size, I = dims->intermediate_size;
+    if (!w->gate_up_i4 || !w->gate_up_i4_scales || !w->down_i4 || !w->down_i4_scales || w->i4_group != FFN_INT4_GROUP)
+        return fail(FFN_ERR_CONFIG, "ffn_decode_layer: the layer carries no INT4 operands");
+    if (!w->post_norm_w) return fail(FFN_ERR_CONFIG, "ffn_decode_layer: the layer has no post-norm weight");
+    if (!(dims->rms_eps > 0.0f)) return fail(FFN_ERR_CONFIG, "ffn_decode_layer: invalid shape or epsilon");
+    FusedTp t = {};
+    const FusedTp *tp = nullptr;
+    if (c && c->tp > 1) {
+        t.tp = c->tp; t.rank = c->rank; t.peer_slots = c->d_slots; t.peer_flags = c->d_flags;
+        t.slot_stride = c->max_tokens * c->hidden; t.max_ctas = kTpMaxCtas; t.seq = (unsigned *)(c->local + 1024);
+        tp = &t;
+    }
+    uint16_t *normed = (uint16_t *)ws;
+    uint16_t *act = normed + (size_t)tokens * H + (size_t)2 * tokens * I;
+    FusedNorm norm = {w->post_norm_w, dims->rms_eps, dims->norm_style == 0};
+    /* 1-2 tokens: norm, FFN, cross-rank reduce and residual update in ONE launch */
+    int st = fused_ffn_launch(stream, h, act, layer_out, w, tokens, H, I, tp, h, &norm);
+    if (st != FFN_NOT_ADMITTED) return st;
+    if (tokens > 64) return fail(FFN_ERR_CONFIG, "ffn_decode_layer: at most 64 tokens per call");
+    st = gemma_rms_norm(normed, h, w->post_norm_w, H, tokens, dims->rms_eps, dims->norm_style == 0, stream);
+    if (st) return st;
+    unsigned *status = nullptr;
+    if ((st = fused_status_word(&status))) return st;
+    st = mma_ffn_launch(stream, normed, act, layer_out, w, tokens, H, I, tp, h, status);
+    if (st == FFN_NOT_ADMITTED) return fail(FFN_ERR_CONFIG, "ffn_decode_layer: no kernel takes tokens=%d H=%d I=%d", tokens, H, I);
+    return st;
+}
+
+int ffn_decode_stack(FfnTpComm *comm, void *stream, void *h, void *ws, void *layer_out, const FfnMlpWeights *layers,
+                     int num_layers, int tokens, const FfnModelDims *dims) {
+    clear_error();
+    TpComm *c = (TpComm *)comm;
+    if (!h || !ws || !layer_out || !layers || !dims) return fail(FFN_ERR_CONFIG, "ffn_decode_stack: null argument");
+    if (num_layers < 0) return fail(FFN_ERR_CONFIG, "ffn_decode_stack: negative layer count");
+    if (c && !c->connected) return fail(FFN_ERR_STATE, "ffn_decode_stack: the communicator is not connected");
+    if (c && c->tp > 1 && (dims->hidden_size != c->hidden || tokens > c->max_tokens))
+        return fail(FFN_ERR_CONFIG, "ffn_decode_stack: the communicator was built for hidden %d and at most %d tokens", c->hidden, c->max_tokens);
+    const int limit = dims->max_chunk > 0 ? dims->max_chunk : 128;
+    if (tokens < 1 || tokens > limit) return fail(FFN_ERR_CONFIG, "ffn_decode_stack: Layer token count exceeds the model's max_chunk");
+    const int H = dims->hidden_size, I = dims->intermediate_size;
+    if (H <= 0 || I <= 0 || H % FFN_INT4_GROUP || I % FFN_INT4_GROUP)
+        return fail(FFN_ERR_CONFIG, "ffn_decode_stack: hidden=%d / intermediate=%d are not whole numbers of %d-wide groups", H, I, FFN_INT4_GROUP);
+    for (int l = 0; l < num_layers; ++l) {
+        const int st = decode_layer(c, (cudaStream_t)stream, h, ws, layer_out, layers + l, tokens, dims);
+        if (st) return st;
+    }
+    return FFN_OK;
 }
 
 }  // extern "C"

@@ -63,6 +63,7 @@ def _declare(lib):
         "ffn_tp_connect_local": [ctypes.POINTER(vp), ci],
         "ffn_tp_destroy": [vp],
         "ffn_forward_mlp_tp": [vp, vp, vp, vp, vp, ctypes.POINTER(MlpWeights), ci, ctypes.POINTER(ModelDims), vp],
+        "ffn_decode_stack": [vp, vp, vp, vp, vp, ctypes.POINTER(MlpWeights), ci, ci, ctypes.POINTER(ModelDims)],
         "ffn_sha256_hex": [vp, ctypes.c_size_t, vp],
         "ffn_quant_manifest_parse": [ctypes.c_char_p, ctypes.POINTER(vp)],
         "ffn_quant_manifest_counts": [vp] + [ctypes.POINTER(ci)] * 4,

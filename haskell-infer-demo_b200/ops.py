@@ -183,3 +183,17 @@ class TpComm:
         if self.handle:
             load().ffn_tp_destroy(self.handle)
             self.handle = None
+
+
+def decode_stack(mlps, h, comm=None, ws=None, layer_out=None):
+    """h <- h + FFN_l(RMSNorm_l(h)) over the layers in ``mlps`` (DenseMlp objects with a post-norm
+    weight), in place; ``comm`` is a TpComm (None = TP 1).  Returns h."""
+    tokens = h.shape[0]
+    first = mlps[0]
+    ws = first.workspace(tokens) if ws is None else ws
+    layer_out = torch.empty((tokens, first.hidden), dtype=torch.bfloat16,
+                            device=first.device) if layer_out is None else layer_out
+    arr = (MlpWeights * len(mlps))(*[m.weights for m in mlps])
+    check(load().ffn_decode_stack(comm.handle if comm is not None else None, _stream(), _ptr(h), _ptr(ws),
+                                  _ptr(layer_out), arr, len(mlps), tokens, ctypes.byref(first.dims)))
+    return h

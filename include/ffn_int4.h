@@ -210,6 +210,19 @@ int ffn_tp_destroy(FfnTpComm *comm);
 int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *ws, void *layer_out,
                        const FfnMlpWeights *w, int tokens, const FfnModelDims *dims, void *residual);
 
+/* The decode stack's FFN sublayers with identity mixers: for l in 0..num_layers-1,
+ *     h <- bf16( f32(h) + f32( FFN_l( RMSNorm_l(h) ) ) )
+ * which is what forward_replicated does per layer on this path - forward_ffn per rank, allreduce of
+ * the layer output, residual_add_device (csrc/engine.cu:1603-1657, 1428-1452) - with the norm of
+ * forward_mlp (csrc/kernels/layers.cu:149-160).  `layers[l]` are the rank-local operands including
+ * post_norm_w; `h` is bf16 [tokens][H], updated in place and replicated on every rank; `layer_out`
+ * receives the last layer's reduced FFN output; `ws` as for ffn_forward_mlp.  With 1 or 2 tokens a
+ * layer is ONE kernel launch (norm, both projections, SiLU*up, cross-rank reduce and residual update
+ * fused); with 3..64 tokens it is the norm kernel plus the tensor-core pair.  comm == NULL or a
+ * communicator of one rank means TP = 1.  Every rank makes the same call. */
+int ffn_decode_stack(FfnTpComm *comm, void *stream, void *h, void *ws, void *layer_out,
+                     const FfnMlpWeights *layers, int num_layers, int tokens, const FfnModelDims *dims);
+
 /* ------------------------------------------------------------------------------------------- */
 /* The artifact path: sidecar manifest, digests, shard views, per-rank load                        */
 /* ------------------------------------------------------------------------------------------- */

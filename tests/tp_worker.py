@@ -73,6 +73,32 @@ def main():
             print(f"config {cfg} M={tokens} TP={world}: max-abs {max_abs:.3g} rel-L2 {rel:.3g} "
                   f"(the reference's BF16 leader reduce would sit at rel-L2 {o.compare(ref_tp, want)[1]:.3g})",
                   flush=True)
+    # config-4 style stack under TP: norm + FFN + reduce + residual per layer, all ranks identical
+    from haskell_infer_demo_b200.ops import decode_stack
+    for tokens in (1, 8):
+        hidden, inter, nl = 1024, 3072, 6
+        if (inter // world) % 128:
+            break
+        h0, layers = o.draw_config(hidden, inter, 4, tokens=tokens, layers=nl, with_norm=True)
+        ref = o.stack(layers, h0)
+        mlps = [upload_layer(lay, dev, tp=world, rank=rank, with_norm=True) for lay in layers]
+        if hidden not in comms:
+            comms[hidden] = TpComm.over_process_group(hidden, 64)
+        inputs = [h0] + ref[:-1]
+        for l in range(nl):                       # teacher-forced per layer
+            h = dev_bf16(inputs[l], dev).clone()
+            decode_stack([mlps[l]], h, comm=comms[hidden])
+            L.device_status()
+            assert_ffn_close(host_f32(h), ref[l], f"stack layer {l} M={tokens} TP={world}")
+        h = dev_bf16(h0, dev).clone()
+        decode_stack(mlps, h, comm=comms[hidden])
+        L.device_status()
+        gathered = [torch.empty_like(h) for _ in range(world)]
+        dist.all_gather(gathered, h)
+        for r in range(world):
+            assert torch.equal(gathered[r].view(torch.int16), h.view(torch.int16)), f"rank {r} differs"
+        if rank == 0:
+            print(f"stack M={tokens} TP={world}: free-running rel-L2 {o.compare(host_f32(h), ref[-1])[1]:.3g}", flush=True)
     dist.barrier()
     for c in comms.values():
         c.close()
