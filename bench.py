@@ -153,16 +153,32 @@ def run_ours(args):
     tp, m, h, i = world, args.tokens, HIDDEN, INTER
     per_rank_bytes = algorithmic_bytes(h, i, tp)
     copies = max(2, int(2.2 * L2_BYTES / per_rank_bytes) + 1)
+    if args.layers > 0:
+        copies = args.layers
     base = make_rank_layer(dev, h, i, tp, rank, seed=2)
     layers = [base] + [clone_layer(base) for _ in range(copies - 1)]
+    if args.layers > 0:  # every layer gets a Gemma norm weight ~ N(0, 0.1)
+        import torch as _t
+        from haskell_infer_demo_b200.ops import DenseMlp, decode_stack
+        g = _t.Generator(device=dev)
+        g.manual_seed(99)
+        layers = [DenseMlp(*lay.tensors[:4], post_norm_w=(_t.randn(h, generator=g, device=dev) * 0.1).to(_t.bfloat16))
+                  for lay in layers]
     comm = TpComm.over_process_group(h, max(m, 2)) if world > 1 else None
+    nl = max(args.layers, 1)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234)
     x = torch.randn((m, h), generator=gen, device=dev).to(torch.bfloat16)
     ws = base.workspace(m)
     out = torch.empty((m, h), dtype=torch.bfloat16, device=dev)
 
+    hstate = x.clone()
+
     def step(k):
+        if args.layers > 0:
+            hstate.copy_(x)  # restart the residual stream so its magnitude does not drift over the run
+            decode_stack(layers, hstate, comm=comm, ws=ws, layer_out=out)
+            return
         lay = layers[k % copies]
         if comm is None:
             lay.forward_mlp_prepared(x, ws=ws, layer_out=out)
@@ -215,12 +231,16 @@ def run_ours(args):
     def e2e_step(k):
         x_dev.copy_(x_host, non_blocking=True)
         lay = layers[k % copies]
-        if comm is None:
+        if args.layers > 0:
+            decode_stack(layers, x_dev, comm=comm, ws=ws, layer_out=out)
+            y_host.copy_(x_dev, non_blocking=True)
+        elif comm is None:
             lay.forward_mlp_prepared(x_dev, ws=ws, layer_out=out)
+            y_host.copy_(out, non_blocking=True)
         else:
             comm.forward_mlp(lay, x_dev, ws=ws, layer_out=out)
-        y_host.copy_(out, non_blocking=True)
-        cur.synchronize()
+            y_host.copy_(out, non_blocking=True)
+        cur.synchronize()  # the caller needs this step's result before it can issue the next one
 
     for k in range(3):
         e2e_step(k)
@@ -241,7 +261,7 @@ def run_ours(args):
     e2e_us = e2e_ms * 1e3 / e2e_steps
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
-        gbs = per_rank_bytes / us_step / 1e3
+        gbs = nl * per_rank_bytes / us_step / 1e3
         line = {
             "metric": METRIC, "value": round(us_step, 3), "unit": "us/step", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(us_step / 1e3, 6),
@@ -249,18 +269,19 @@ def run_ours(args):
             "data": "synthetic (N(0,0.02) weights quantized on the device, N(0,1) BF16 activations)",
             "tokens_per_s": round(m * 1e6 / us_step, 1),
             "hbm_gbs_per_gpu": round(gbs, 1), "pct_of_8tbs": round(gbs / 80.0, 2),
-            "config": {"workload": f"27B-shape INT4 FFN decode H={h} I={i} M={m} TP={tp} (BASELINE configs[2])",
+            "config": {"workload": (f"27B-shape INT4 FFN decode H={h} I={i} M={m} TP={tp} (BASELINE configs[2])" if not args.layers else
+                                    f"{args.layers}-layer stack h+=FFN(GemmaRMSNorm(h)), H={h} I={i} M={m} TP={tp} (BASELINE configs[4])"),
                        "l2": f"rotating {copies} weight copies per rank ({copies * per_rank_bytes / 1e6:.0f} MB > 2x L2)",
                        "timing": f"{args.steps} steps in one CUDA graph, median of {reps} replays, max over ranks"},
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(gbs / peak, 4), "peak_source": peak_kind, "traffic": TRAFFIC_BYTES.get((tp, m)),
-                         "algorithmic_bytes_per_launch": per_rank_bytes},
+                         "frac": round(gbs / peak, 4), "peak_source": peak_kind, "traffic": TRAFFIC_BYTES.get((tp, m)) if not args.layers else None,
+                         "algorithmic_bytes_per_launch": per_rank_bytes, "launches_per_step": nl},
             "e2e": {"value": round(e2e_us, 3), "unit": "us/step", "h2d_bytes_per_step": m * h * 2,
                     "d2h_bytes_per_step": m * h * 2},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * nl * (1 if m <= 2 else 4),
             "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu:
+        if world == 1 and not args.no_cpu and not args.layers:
             line["cpu_baseline"] = cpu_baseline(h, i, m, budget_s=12.0)
         print(json.dumps(line), flush=True)
     if comm is not None:
@@ -360,6 +381,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="0: one FFN per step (the headline workload).  L > 0: a step is one pass of h <- h + "
+                         "FFN_l(RMSNorm_l(h)) through L independent layers (BASELINE configs[4] at L=64)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

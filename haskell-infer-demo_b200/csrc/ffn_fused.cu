@@ -160,6 +160,9 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void red_release_sys_add(unsigned *p, unsigned v) {
     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -661,15 +664,19 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
             /* publish this CTA's rows to every rank, wait for every rank's, add in rank order */
             __threadfence_system();
             __syncwarp();
-            if (lane < P.tp) red_release_sys_add(P.peer_flags[lane] + blockIdx.x, 1u);
-            const unsigned want = (seq + 1u) * (unsigned)P.tp;
+            /* lane r tells rank r, then watches rank r's word in this rank's own array */
+            const unsigned want = seq + 1u;
+            const size_t word = (size_t)blockIdx.x * kTpMaxRanks;
+            if (lane < P.tp) st_release_sys(P.peer_flags[lane] + word + P.rank, want);
             bool arrived = false;
             if (ok) {
+                bool mine_in = lane >= P.tp;
                 for (uint32_t i = 0; i < kSpinLimit; ++i) {
-                    if ((int)(ld_acquire_sys(P.peer_flags[P.rank] + blockIdx.x) - want) >= 0) { arrived = true; break; }
+                    if (!mine_in) mine_in = (int)(ld_acquire_sys(P.peer_flags[P.rank] + word + lane) - want) >= 0;
+                    if (__all_sync(0xFFFFFFFFu, mine_in)) { arrived = true; break; }
                     __nanosleep(20);
                 }
-                if (!arrived) give_up(sm, P.sync, ST_PEER_FLAG);
+                if (!arrived && lane == 0) give_up(sm, P.sync, ST_PEER_FLAG);
             }
             if (arrived) {
                 const float *mine = P.peer_slots[P.rank] + (size_t)(seq & 1u) * P.tp * P.slot_stride;

@@ -275,20 +275,29 @@ __global__ void __launch_bounds__(kMmaThreads) down_mma_kernel(const MmaParams P
         /* publish this CTA's rows on every rank, wait (bounded) for every rank's, add in rank order */
         __threadfence_system();
         __syncthreads();
-        if (threadIdx.x < P.tp)
-            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(P.peer_flags[threadIdx.x] + blockIdx.x) : "memory");
-        const unsigned want = (seq + 1u) * (unsigned)P.tp;
+        /* thread r tells rank r (a store of the call number, not a count), then watches rank r's word */
+        const unsigned want = seq + 1u;
+        const size_t word = (size_t)blockIdx.x * kTpMaxRanks;
         __shared__ int arrived;
-        if (threadIdx.x == 0) {
+        if (threadIdx.x < 32) {
+            const int lane = threadIdx.x;
+            if (lane < P.tp)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.peer_flags[lane] + word + P.rank), "r"(want) : "memory");
+            bool mine_in = lane >= P.tp;
             int ok = 0;
             for (uint32_t i = 0; i < kMmaSpinLimit; ++i) {
-                unsigned v;
-                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(P.peer_flags[P.rank] + blockIdx.x) : "memory");
-                if ((int)(v - want) >= 0) { ok = 1; break; }
+                if (!mine_in) {
+                    unsigned v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(P.peer_flags[P.rank] + word + lane) : "memory");
+                    mine_in = (int)(v - want) >= 0;
+                }
+                if (__all_sync(0xFFFFFFFFu, mine_in)) { ok = 1; break; }
                 __nanosleep(40);
             }
-            if (!ok) atomicCAS(P.status, 0u, 6u | ((unsigned)blockIdx.x << 8)); /* 6 = peer arrival flag */
-            arrived = ok;
+            if (lane == 0) {
+                if (!ok) atomicCAS(P.status, 0u, 6u | ((unsigned)blockIdx.x << 8)); /* 6 = peer arrival word */
+                arrived = ok;
+            }
         }
         __syncthreads();
         if (arrived) {

@@ -27,11 +27,23 @@ int gemm_int4_dispatch(const void *a, const void *packed, const void *scales, vo
 int fused_ffn_try(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                   const FfnMlpWeights *w, int tokens, int H, int I);
 
+/* Layout of one rank's exchange buffer:
+ *   [ arrival words: kTpMaxCtas x kTpMaxRanks x u32 | call counter u32, pad | slots ]
+ * Word [c][r] holds the number of the last call for which rank r's "CTA c" has delivered its rows
+ * (a plain store of call number + 1, never a count).  A waiter compares every sender's word with
+ * its own call number, so the test does not depend on which kernels served the earlier calls: the
+ * single-pass kernel (one arrival per SM) and the batched kernels (one per 32 output rows) use
+ * different subsets of the words and may alternate freely on one communicator. */
+constexpr int kTpMaxCtas = 256;
+constexpr int kTpMaxRanks = 16;
+constexpr size_t kTpSeqOffset = (size_t)kTpMaxCtas * kTpMaxRanks * sizeof(unsigned);
+constexpr size_t kTpFlagBytes = kTpSeqOffset + 256;
+
 /* Tensor-parallel exchange tables (device arrays of per-rank pointers, set up once at load). */
 struct FusedTp {
     int tp, rank;
     float *const *peer_slots;    /* [tp] -> each rank's [2][tp][slot_stride] fp32 */
-    unsigned *const *peer_flags; /* [tp] -> each rank's per-CTA arrival counters */
+    unsigned *const *peer_flags; /* [tp] -> each rank's arrival words [kTpMaxCtas][kTpMaxRanks] */
     int slot_stride;             /* floats per (parity, rank) slot */
     unsigned *seq;               /* this rank's call counter for this communicator (device word) */
     int max_ctas;                /* grid size every rank uses */

@@ -6,11 +6,12 @@
  * (csrc/collective.cu:108-144, 168-219) for this path: no staging copies, no host-issued adds.
  *
  * One exchange buffer per rank, one allocation:
- *     [ flags: kTpMaxCtas x u32 | call counter u32, pad to 2 KiB | slots: 2 x tp x max_tokens*hidden x f32 ]
- * flags[c] counts arrivals of "CTA c" from every rank (monotonic; the kernel derives its target from
- * a device-resident call counter, so replaying a captured graph stays correct).  Slots are double
- * buffered by call parity: a rank can be at most one call ahead of a peer, because completing a
- * call needs every peer's flag increment for that call.
+ *     [ arrival words: kTpMaxCtas x kTpMaxRanks x u32 | call counter u32, pad | slots: 2 x tp x max_tokens*hidden x f32 ]
+ * Word [c][r] is the number (+1) of the last call for which rank r's "CTA c" delivered its rows; the
+ * kernel compares it with a device-resident call counter, so replaying a captured graph stays
+ * correct and kernels with different grids can share the communicator.  Slots are double buffered
+ * by call parity: a rank can be at most one call ahead of a peer, because completing a call needs
+ * every peer's arrival for that call.
  */
 #include <string.h>
 
@@ -21,9 +22,6 @@
 
 namespace ffn {
 
-constexpr int kTpMaxCtas = 256;
-constexpr int kTpMaxRanks = 16;
-constexpr size_t kTpFlagBytes = 2048; /* flags in the first KiB, this rank's call counter at +1024 */
 
 struct TpComm {
     int tp = 0, rank = 0, hidden = 0, max_tokens = 0, device = 0;
@@ -184,7 +182,7 @@ int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *
     t.tp = c->tp; t.rank = c->rank;
     t.peer_slots = c->d_slots; t.peer_flags = c->d_flags;
     t.slot_stride = c->max_tokens * c->hidden;
-    t.seq = (unsigned *)(c->local + 1024);
+    t.seq = (unsigned *)(c->local + kTpSeqOffset);
     t.max_ctas = kTpMaxCtas;
     uint16_t *act = (uint16_t *)ws + (size_t)tokens * H + (size_t)2 * tokens * I;
     int st = fused_ffn_launch((cudaStream_t)stream, normed, act, layer_out, w, tokens, H, I, &t, residual, nullptr);
@@ -211,7 +209,7 @@ static int decode_layer(TpComm *c, cudaStream_t stream, void *h, void *ws, void 
     const FusedTp *tp = nullptr;
     if (c && c->tp > 1) {
         t.tp = c->tp; t.rank = c->rank; t.peer_slots = c->d_slots; t.peer_flags = c->d_flags;
-        t.slot_stride = c->max_tokens * c->hidden; t.max_ctas = kTpMaxCtas; t.seq = (unsigned *)(c->local + 1024);
+        t.slot_stride = c->max_tokens * c->hidden; t.max_ctas = kTpMaxCtas; t.seq = (unsigned *)(c->local + kTpSeqOffset);
         tp = &t;
     }
     uint16_t *normed = (uint16_t *)ws;

@@ -47,6 +47,7 @@ def main():
             comms[h] = TpComm.over_process_group(h, 64)
         comm = comms[h]
         xd = dev_bf16(x, dev)
+        dist.barrier()      # host-side oracle work differs per rank; the kernel's peer wait is bounded (~0.2 s)
         got_t = comm.forward_mlp(mlp, xd)
         L.device_status()
         got = host_f32(got_t)
@@ -75,7 +76,7 @@ def main():
                   flush=True)
     # config-4 style stack under TP: norm + FFN + reduce + residual per layer, all ranks identical
     from haskell_infer_demo_b200.ops import decode_stack
-    for tokens in (1, 8):
+    for tokens in (1, 8, 2):      # single-pass and batched kernels alternate on one communicator
         hidden, inter, nl = 1024, 3072, 6
         if (inter // world) % 128:
             break
@@ -87,10 +88,12 @@ def main():
         inputs = [h0] + ref[:-1]
         for l in range(nl):                       # teacher-forced per layer
             h = dev_bf16(inputs[l], dev).clone()
+            dist.barrier()
             decode_stack([mlps[l]], h, comm=comms[hidden])
             L.device_status()
             assert_ffn_close(host_f32(h), ref[l], f"stack layer {l} M={tokens} TP={world}")
         h = dev_bf16(h0, dev).clone()
+        dist.barrier()
         decode_stack(mlps, h, comm=comms[hidden])
         L.device_status()
         gathered = [torch.empty_like(h) for _ in range(world)]
