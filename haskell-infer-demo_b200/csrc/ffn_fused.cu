@@ -206,16 +206,21 @@ struct XChunk {
     float fac;
 };
 
-__device__ __forceinline__ void prepare_chunk(XChunk &xc, const uint16_t *src /* shared, 64-byte aligned */, bool on,
-                                              const uint16_t *norm_w = nullptr /* global, this chunk's 32 weights */,
-                                              float inv_rms = 1.0f, float gemma = 0.0f) {
-    uint32_t v[16];
+/* The 32 BF16 values of one slice (64-byte aligned): from global memory (x, present when the kernel
+ * starts) or from the shared-memory copy of act the producer fetched. */
+template <bool GLOBAL>
+__device__ __forceinline__ void load_chunk(uint32_t (&v)[16], const uint16_t *src, bool on) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         uint4 t = make_uint4(0, 0, 0, 0);
-        if (on) t = lds16(src + q * 8);
+        if (on) t = GLOBAL ? __ldg((const uint4 *)(src + q * 8)) : lds16(src + q * 8);
         v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
     }
+}
+
+__device__ __forceinline__ void prepare_chunk(XChunk &xc, uint32_t (&v)[16], bool on,
+                                              const uint16_t *norm_w = nullptr /* global, this chunk's 32 weights */,
+                                              float inv_rms = 1.0f, float gemma = 0.0f) {
     if (norm_w != nullptr && on) { /* fused RMSNorm: the reference's expression and its BF16 rounding */
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -329,8 +334,9 @@ __device__ __forceinline__ void give_up(Smem *sm, unsigned *sync, int where) {
     atomicCAS(sync + 3, 0u, (unsigned)where | ((unsigned)blockIdx.x << 8));
 }
 
+/* first row of CTA `cta`'s contiguous share; total * ctas < 2^32 is checked on the host */
 __device__ __forceinline__ int cta_begin(int total, int cta, int ctas) {
-    return (int)(((long long)total * cta) / ctas);
+    return (int)(((unsigned)total * (unsigned)cta) / (unsigned)ctas);
 }
 
 __device__ __forceinline__ void stamp(const FusedParams &P, int slot) {
@@ -354,11 +360,23 @@ __device__ __forceinline__ void consume_phase(const FusedParams &P, const PhaseP
     const int row_end = cta_begin(pl.rows_total, blockIdx.x + 1, gridDim.x);
     const int ntiles = (row_end - row_begin + pl.TR - 1) / pl.TR;
 
-    /* this thread's slice of the activation vector(s): wait for it in shared memory, convert */
-    if (!mbar_wait<100>(&sm->x_full[PAIRS ? 0 : 1], 0u, &sm->abort_flag)) {
+    /* This thread's 32-element slice(s) of the activation vector(s).  Phase 1 reads x straight from
+     * global memory: it is there when the kernel starts, so the loads are in flight while the
+     * producer is still setting up.  Phase 2 waits for the copy of act the producer brings into
+     * shared memory once the grid barrier has opened. */
+    if (!PAIRS && !mbar_wait<64>(&sm->x_full[1], 0u, &sm->abort_flag)) {
         give_up(sm, P.sync, ST_X_FULL);
         return;
     }
+    const uint16_t *src = PAIRS ? P.x : xs;
+    uint32_t xv[CIT][MT][16];
+#pragma unroll
+    for (int c = 0; c < CIT; ++c)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const int col = ct + c * pl.CT;
+            load_chunk<PAIRS>(xv[c][m], src + (size_t)m * pl.K + (size_t)min(col, pl.cpr - 1) * 32, active && col < pl.cpr);
+        }
     float inv_rms[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) inv_rms[m] = 1.0f;
@@ -367,11 +385,15 @@ __device__ __forceinline__ void consume_phase(const FusedParams &P, const PhaseP
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             float ss = 0.0f;
-            const uint32_t *row = (const uint32_t *)(xs + (size_t)m * pl.K);
-            for (int i = ti; i < pl.K / 2; i += kConsumerThreads) {
-                const uint32_t pr = row[i];
-                ss = fmaf(bf16_lo(pr), bf16_lo(pr), ss);
-                ss = fmaf(bf16_hi(pr), bf16_hi(pr), ss);
+            if (rg == 0) { /* row group 0 covers every slice exactly once; absent slices hold zeros */
+#pragma unroll
+                for (int c = 0; c < CIT; ++c)
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t pr = xv[c][m][i];
+                        ss = fmaf(bf16_lo(pr), bf16_lo(pr), ss);
+                        ss = fmaf(bf16_hi(pr), bf16_hi(pr), ss);
+                    }
             }
             ss = warp_sum(ss);
             if (lane == 0) sm->norm_red[m][ti >> 5] = ss;
@@ -392,7 +414,7 @@ __device__ __forceinline__ void consume_phase(const FusedParams &P, const PhaseP
         for (int m = 0; m < MT; ++m) {
             const int col = ct + c * pl.CT;
             const bool on = active && col < pl.cpr;
-            prepare_chunk(xc[c][m], xs + (size_t)m * pl.K + (size_t)col * 32, on,
+            prepare_chunk(xc[c][m], xv[c][m], on,
                           normalize ? P.norm_w + (size_t)min(col, pl.cpr - 1) * 32 : nullptr, inv_rms[m],
                           P.norm_gemma ? 1.0f : 0.0f);
         }
@@ -565,15 +587,11 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
              * so replaying a captured graph or changing the grid size needs no host bookkeeping) */
             const unsigned bar_target = P.sync[1] + gridDim.x;
             stamp(P, 1);
-            /* the activation vector of phase 1 */
-            mbar_expect_tx(&sm->x_full[0], (uint32_t)(P.M * P.H * 2));
-            bulk_g2s(xs, P.x, (uint32_t)(P.M * P.H * 2), &sm->x_full[0]);
             const int total = nt1 + nt2;
             int t = 0;
             bool act_issued = false, failed = false;
             /* Phase 2's activation vector is fetched once the grid barrier has opened (every CTA has
-             * stored its rows of act).  Phase 1's x is dead by then: this CTA's consumers finished
-             * phase 1 before its epilogue arrived at the barrier. */
+             * stored its rows of act). */
             auto fetch_act = [&]() {
                 bool open = false;
                 for (uint32_t i = 0; i < kSpinLimit && !open; ++i) {
@@ -636,9 +654,9 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
                 for (uint32_t i = 0; i < kSpinLimit && !done; ++i) done = mbar_try_wait(&sm->full[u % ns], (uint32_t)(u / ns) & 1u);
                 if (!done) atomicCAS(P.sync + 3, 0u, (unsigned)ST_DRAIN | ((unsigned)blockIdx.x << 8));
             }
-            for (int k = 0; k < (act_issued ? 2 : 1); ++k) {
+            if (act_issued) {
                 bool done = false;
-                for (uint32_t i = 0; i < kSpinLimit && !done; ++i) done = mbar_try_wait(&sm->x_full[k], 0u);
+                for (uint32_t i = 0; i < kSpinLimit && !done; ++i) done = mbar_try_wait(&sm->x_full[1], 0u);
                 if (!done) atomicCAS(P.sync + 3, 0u, (unsigned)ST_DRAIN | ((unsigned)blockIdx.x << 8));
             }
         }
@@ -792,6 +810,7 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
                      const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual,
                      const FusedNorm *norm) {
     if (tokens < 1 || tokens > 2) return FFN_NOT_ADMITTED;
+    if (H > (1 << 22) || I > (1 << 22)) return FFN_NOT_ADMITTED; /* 32-bit row partitioning in the kernel */
     DeviceState *dp = nullptr;
     const int st = device_state(&dp);
     if (st) return st;
@@ -834,7 +853,7 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
     P.stage_w_bytes = round_up(max(2 * P.p1.TR * P.p1.rb, P.p2.TR * P.p2.rb), 128);
     P.sc_half_bytes = round_up(max(P.p1.TR * P.p1.G * 2, P.p2.TR * P.p2.G * 2) + 32, 16);
     P.stage_bytes = round_up(P.stage_w_bytes + 2 * P.sc_half_bytes, 128);
-    P.xs_bytes = round_up(tokens * max(H, I) * 2, 128);
+    P.xs_bytes = round_up(tokens * I * 2, 128); /* act only: x is read from global memory */
     P.trace = g_trace;
     static const int debug_flags = getenv("FFN_INT4_DEBUG") ? atoi(getenv("FFN_INT4_DEBUG")) : 0;
     P.debug = debug_flags;
@@ -912,6 +931,7 @@ int fused_ffn_launch_noalloc(cudaStream_t stream, const void *normed, void *laye
                              const FfnMlpWeights *w, int tokens, int H, int I) {
     if (tokens < 1 || tokens > 2)
         return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: %d tokens; this entry point takes 1 or 2", tokens);
+    if (H > (1 << 22)) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: hidden size %d is beyond the kernel's range", H);
     if ((long long)tokens * I > kNoAllocActElems)
         return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: tokens * intermediate_size = %lld exceeds the "
                     "static scratch (%d elements)", (long long)tokens * I, kNoAllocActElems);
@@ -943,7 +963,7 @@ int fused_ffn_launch_noalloc(cudaStream_t stream, const void *normed, void *laye
     P.stage_w_bytes = round_up(max(2 * P.p1.TR * P.p1.rb, P.p2.TR * P.p2.rb), 128);
     P.sc_half_bytes = round_up(max(P.p1.TR * P.p1.G * 2, P.p2.TR * P.p2.G * 2) + 32, 16);
     P.stage_bytes = round_up(P.stage_w_bytes + 2 * P.sc_half_bytes, 128);
-    P.xs_bytes = round_up(tokens * max(H, I) * 2, 128);
+    P.xs_bytes = round_up(tokens * I * 2, 128); /* act only: x is read from global memory */
     const size_t fixed = ((sizeof(Smem) + 127) / 128) * 128 + (size_t)P.xs_bytes;
     if (P.p1.TR * 2 * tokens * P.p1.nhw > kPartFloats || P.p2.TR * tokens * P.p2.nhw > kPartFloats ||
         fixed + 2 * (size_t)P.stage_bytes > (size_t)d.smem_optin)

@@ -50,7 +50,7 @@ def test_ffn_matches_oracle(cuda, drawn, cfg, tokens, fused):
 
 def test_fused_is_deterministic_and_repeatable(cuda, drawn):
     """Same inputs, many launches: bit-identical outputs (fixed-order reductions, self-resetting
-    grid barrier) and the activation left in the workspace equals the oracle's within one ulp."""
+    hand-over buffers) and the activation left in the workspace equals the oracle's within one ulp."""
     x, layer, want = drawn(1, 1)
     mlp = upload_layer(layer, cuda)
     xd = dev_bf16(x, cuda)
@@ -64,6 +64,18 @@ def test_fused_is_deterministic_and_repeatable(cuda, drawn):
     h, i = layer.hidden, layer.inter
     got_act = host_f32(ws[h + 2 * i:h + 3 * i].view(1, i))
     assert o.compare(got_act, act)[1] <= 5e-3
+
+
+def test_fused_shapes_alternate(cuda, drawn):
+    """Launches of different shapes and token counts follow each other on one device: the buffers
+    that hand act from phase 1 to phase 2 must never show a later launch an earlier launch's values."""
+    order = [(2, 2), (0, 1), (2, 1), (1, 2), (0, 2), (2, 2), (1, 1), (2, 1)]
+    mlps = {key: upload_layer(drawn(*key)[1], cuda) for key in set(order)}   # the draw depends on the token count
+    for cfg, tokens in order:
+        x, _, want = drawn(cfg, tokens)
+        got = host_f32(mlps[(cfg, tokens)].forward_mlp_prepared(dev_bf16(x, cuda)))
+        L.device_status()
+        assert_ffn_close(got, want, f"config {cfg} M={tokens} in a mixed sequence")
 
 
 def test_config0_golden_output(cuda):
