@@ -153,7 +153,7 @@ int ffn_int4_device_status(int *where, int *cta) {
     if (st != 0) {
         static const char *names[] = {"", "producer waiting for a free stage", "consumer waiting for weights",
                                       "consumer waiting for a partial slot", "epilogue waiting for partials",
-                                      "grid barrier", "peer arrival flag", "draining copies",
+                                      "grid barrier", "a peer rank's partial sums", "draining copies",
                                       "consumer waiting for the activation vector"};
         const unsigned w = st & 0xFF;
         return fail(FFN_ERR_CUDA, "a bounded device-side wait ran out (%s, CTA %u); the kernel returned early and "

@@ -79,9 +79,8 @@ struct FusedParams {
                              [2] unused, [3] status */
     /* tensor parallelism (tp == 1: unused) */
     int tp, rank;
-    float *const *peer_slots;   /* device array [tp]: each rank's [2][tp][M_max][H] fp32 slots */
-    unsigned *const *peer_flags;/* device array [tp]: each rank's per-CTA arrival counters */
-    int slot_stride;      /* floats per (parity, rank) slot = M_max * H */
+    unsigned long long *const *peer_slots; /* device array [tp]: each rank's [2][tp][M_max][H] tagged words */
+    int slot_stride;      /* elements per (parity, rank) slot = M_max * H */
     unsigned *tp_seq;     /* this communicator's call counter (slot parity, flag target) */
     /* optional fused residual update with the reduced output y: h <- bf16(h + y); NULL = off */
     uint16_t *residual;
@@ -153,22 +152,6 @@ __device__ __forceinline__ uint4 lds16(const void *p) {
 __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned *p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ void red_release_sys_add(unsigned *p, unsigned v) {
-    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ float ld_relaxed_sys_f32(const float *p) {
-    float v;
-    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ uint32_t lop3_and_xor(uint32_t a, uint32_t b, uint32_t c) {
@@ -545,7 +528,7 @@ __device__ __forceinline__ bool epilogue_phase(const FusedParams &P, const Phase
                         f32_to_bf16_bits(bf16_bits_to_f32(P.residual[(size_t)m * P.H + row]) + y);
             } else {
                 const size_t off = (size_t)((seq & 1u) * P.tp + P.rank) * P.slot_stride + (size_t)m * P.H + row;
-                for (int r = 0; r < P.tp; ++r) P.peer_slots[r][off] = a; /* own slot on every rank */
+                for (int r = 0; r < P.tp; ++r) tp_store_tagged(P.peer_slots[r] + off, a, seq + 1u); /* own slot on every rank */
             }
         }
         __syncwarp();
@@ -679,29 +662,27 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
         if (ok) ok = epilogue_phase<MT, false>(P, P.p2, sm, nt1, seq);
         if (lane == 0) stamp(P, 10);
         if (P.tp > 1) {
-            /* publish this CTA's rows to every rank, wait for every rank's, add in rank order */
-            __threadfence_system();
-            __syncwarp();
-            /* lane r tells rank r, then watches rank r's word in this rank's own array */
-            const unsigned want = seq + 1u;
-            const size_t word = (size_t)blockIdx.x * kTpMaxRanks;
-            if (lane < P.tp) st_release_sys(P.peer_flags[lane] + word + P.rank, want);
-            bool arrived = false;
+            /* every rank's partial sums of this CTA's rows arrive in this rank's own buffer as
+             * tagged words (sent tile by tile during phase 2): wait for each, add in rank order */
             if (ok) {
-                bool mine_in = lane >= P.tp;
-                for (uint32_t i = 0; i < kSpinLimit; ++i) {
-                    if (!mine_in) mine_in = (int)(ld_acquire_sys(P.peer_flags[P.rank] + word + lane) - want) >= 0;
-                    if (__all_sync(0xFFFFFFFFu, mine_in)) { arrived = true; break; }
-                    __nanosleep(20);
-                }
-                if (!arrived && lane == 0) give_up(sm, P.sync, ST_PEER_FLAG);
-            }
-            if (arrived) {
-                const float *mine = P.peer_slots[P.rank] + (size_t)(seq & 1u) * P.tp * P.slot_stride;
+                const unsigned long long *mine = P.peer_slots[P.rank] + (size_t)(seq & 1u) * P.tp * P.slot_stride;
                 for (int i = lane; i < (e2 - b2) * MT; i += 32) {
                     const int row = b2 + i / MT, m = i % MT;
                     float a = 0.0f;
-                    for (int r = 0; r < P.tp; ++r) a += ld_relaxed_sys_f32(mine + (size_t)r * P.slot_stride + (size_t)m * P.H + row);
+                    bool all_in = true;
+                    for (int r = 0; r < P.tp && all_in; ++r) {
+                        const unsigned long long *p = mine + (size_t)r * P.slot_stride + (size_t)m * P.H + row;
+                        float v = 0.0f;
+                        bool in = tp_load_tagged(p, seq + 1u, &v);
+                        for (uint32_t k = 0; !in && k < kTpPollLimit; ++k) {
+                            if ((k & 1023u) == 1023u && sm->abort_flag) break; /* another lane already gave up */
+                            __nanosleep(20);
+                            in = tp_load_tagged(p, seq + 1u, &v);
+                        }
+                        all_in = in;
+                        a += v;
+                    }
+                    if (!all_in) { give_up(sm, P.sync, ST_PEER_FLAG); break; }
                     const float y = round_bf16(a);
                     P.out[(size_t)m * P.H + row] = f32_to_bf16_bits(y);
                     if (P.residual)
@@ -834,7 +815,7 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
     }
     if (tp && tp->tp > 1) {
         P.tp = tp->tp; P.rank = tp->rank;
-        P.peer_slots = tp->peer_slots; P.peer_flags = tp->peer_flags; P.slot_stride = tp->slot_stride;
+        P.peer_slots = tp->peer_slots; P.slot_stride = tp->slot_stride;
         P.tp_seq = tp->seq;
         if (tokens * H > tp->slot_stride) return fail(FFN_ERR_CONFIG, "fused FFN: %d tokens exceed the exchange buffer", tokens);
     }
@@ -862,10 +843,7 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
     P.nstages = (int)min((size_t)kMaxStages, ((size_t)d.smem_optin - fixed) / (size_t)P.stage_bytes);
     if (P.nstages < 2) return FFN_NOT_ADMITTED;
     const size_t smem = fixed + (size_t)P.nstages * P.stage_bytes;
-    int grid = d.sm_count;
-    if (tp && tp->tp > 1) {
-        grid = min(grid, tp->max_ctas); /* every rank must use the same grid: CTA c pairs with CTA c */
-    }
+    const int grid = d.sm_count; /* under TP every rank runs the same grid: CTA c owns the same rows everywhere */
 
 #define FFN_LAUNCH(A, B, C) return launch_fused<A, B, C>(d, P, grid, smem, stream)
     if (tokens == 1) {

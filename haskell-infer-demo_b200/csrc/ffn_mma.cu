@@ -33,7 +33,6 @@ constexpr int kMmaThreads = kMmaWarps * 32;
 constexpr int kMmaRows = 32;          /* weight rows per CTA: two 16-row MMA tiles */
 constexpr int kMmaKC = 512;           /* K per pipeline stage: 4 groups */
 constexpr int kWRowBytes = kMmaKC / 2 + 16;   /* 272: conflict-free 32-bit reads down 8 rows */
-constexpr uint32_t kMmaSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
@@ -81,8 +80,7 @@ struct MmaParams {
     uint16_t *residual;       /* down: optional bf16 [M][N], h <- bf16(h + y) */
     /* tensor parallelism (down only) */
     int tp, rank, slot_stride;
-    float *const *peer_slots;
-    unsigned *const *peer_flags;
+    unsigned long long *const *peer_slots;
     unsigned *tp_seq;
     unsigned *status;         /* word 3 of the device's synchronisation words */
 };
@@ -264,7 +262,7 @@ __global__ void __launch_bounds__(kMmaThreads) down_mma_kernel(const MmaParams P
         for (int ks = 0; ks < kMmaWarps; ++ks) y += red[(size_t)(ks * kMmaRows + r) * ldr + m];
         const size_t o = (size_t)m * P.N + row0 + r;
         if (P.tp > 1) {
-            for (int q = 0; q < P.tp; ++q) P.peer_slots[q][slot + o] = y;
+            for (int q = 0; q < P.tp; ++q) tp_store_tagged(P.peer_slots[q] + slot + o, y, seq + 1u);
         } else {
             const float v = round_bf16(y);
             P.out[o] = f32_to_bf16_bits(v);
@@ -272,50 +270,30 @@ __global__ void __launch_bounds__(kMmaThreads) down_mma_kernel(const MmaParams P
         }
     }
     if (P.tp > 1) {
-        /* publish this CTA's rows on every rank, wait (bounded) for every rank's, add in rank order */
-        __threadfence_system();
-        __syncthreads();
-        /* thread r tells rank r (a store of the call number, not a count), then watches rank r's word */
-        const unsigned want = seq + 1u;
-        const size_t word = (size_t)blockIdx.x * kTpMaxRanks;
-        __shared__ int arrived;
-        if (threadIdx.x < 32) {
-            const int lane = threadIdx.x;
-            if (lane < P.tp)
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(P.peer_flags[lane] + word + P.rank), "r"(want) : "memory");
-            bool mine_in = lane >= P.tp;
-            int ok = 0;
-            for (uint32_t i = 0; i < kMmaSpinLimit; ++i) {
-                if (!mine_in) {
-                    unsigned v;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(P.peer_flags[P.rank] + word + lane) : "memory");
-                    mine_in = (int)(v - want) >= 0;
+        /* every rank's partial sums of this CTA's rows arrive in this rank's own buffer as tagged
+         * words: each thread waits (bounded) for the words of its own outputs and adds them in
+         * rank order.  The thread stored its own words above, so no barrier is needed. */
+        const unsigned long long *mine = P.peer_slots[P.rank] + (size_t)(seq & 1u) * P.tp * P.slot_stride;
+        for (int i = threadIdx.x; i < kMmaRows * P.M; i += kMmaThreads) {
+            const int r = i % kMmaRows, m = i / kMmaRows;
+            const size_t o = (size_t)m * P.N + row0 + r;
+            float y = 0.0f;
+            bool all_in = true;
+            for (int q = 0; q < P.tp && all_in; ++q) {
+                const unsigned long long *p = mine + (size_t)q * P.slot_stride + o;
+                float v = 0.0f;
+                bool in = tp_load_tagged(p, seq + 1u, &v);
+                for (uint32_t k = 0; !in && k < kTpPollLimit; ++k) {
+                    __nanosleep(40);
+                    in = tp_load_tagged(p, seq + 1u, &v);
                 }
-                if (__all_sync(0xFFFFFFFFu, mine_in)) { ok = 1; break; }
-                __nanosleep(40);
+                all_in = in;
+                y += v;
             }
-            if (lane == 0) {
-                if (!ok) atomicCAS(P.status, 0u, 6u | ((unsigned)blockIdx.x << 8)); /* 6 = peer arrival word */
-                arrived = ok;
-            }
-        }
-        __syncthreads();
-        if (arrived) {
-            __threadfence_system();
-            const float *mine = P.peer_slots[P.rank] + (size_t)(seq & 1u) * P.tp * P.slot_stride;
-            for (int i = threadIdx.x; i < kMmaRows * P.M; i += kMmaThreads) {
-                const int r = i % kMmaRows, m = i / kMmaRows;
-                const size_t o = (size_t)m * P.N + row0 + r;
-                float y = 0.0f;
-                for (int q = 0; q < P.tp; ++q) {
-                    float v;
-                    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(mine + (size_t)q * P.slot_stride + o) : "memory");
-                    y += v;
-                }
-                const float v = round_bf16(y);
-                P.out[o] = f32_to_bf16_bits(v);
-                if (P.residual) P.residual[o] = f32_to_bf16_bits(bf16_bits_to_f32(P.residual[o]) + v);
-            }
+            if (!all_in) { atomicCAS(P.status, 0u, 6u | ((unsigned)blockIdx.x << 8)); break; } /* 6 = peer data */
+            const float v = round_bf16(y);
+            P.out[o] = f32_to_bf16_bits(v);
+            if (P.residual) P.residual[o] = f32_to_bf16_bits(bf16_bits_to_f32(P.residual[o]) + v);
         }
     }
 }
@@ -400,10 +378,9 @@ int mma_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *lay
     B.tp = 1; B.status = status;
     if (tp && tp->tp > 1) {
         if (tokens * H > tp->slot_stride) return fail(FFN_ERR_CONFIG, "batched INT4 FFN: %d tokens exceed the exchange buffer", tokens);
-        if (H / kMmaRows > tp->max_ctas) return fail(FFN_ERR_CONFIG, "batched INT4 FFN: hidden size %d needs more arrival flags than the communicator has", H);
         A.tp_seq = tp->seq;
         B.tp = tp->tp; B.rank = tp->rank; B.slot_stride = tp->slot_stride;
-        B.peer_slots = tp->peer_slots; B.peer_flags = tp->peer_flags; B.tp_seq = tp->seq;
+        B.peer_slots = tp->peer_slots; B.tp_seq = tp->seq;
     }
     if (tokens <= 8) return launch_pair<1>(A, B, smem_optin, stream);
     if (tokens <= 16) return launch_pair<2>(A, B, smem_optin, stream);

@@ -28,25 +28,37 @@ int fused_ffn_try(cudaStream_t stream, const void *normed, void *act, void *laye
                   const FfnMlpWeights *w, int tokens, int H, int I);
 
 /* Layout of one rank's exchange buffer:
- *   [ arrival words: kTpMaxCtas x kTpMaxRanks x u32 | call counter u32, pad | slots ]
- * Word [c][r] holds the number of the last call for which rank r's "CTA c" has delivered its rows
- * (a plain store of call number + 1, never a count).  A waiter compares every sender's word with
- * its own call number, so the test does not depend on which kernels served the earlier calls: the
- * single-pass kernel (one arrival per SM) and the batched kernels (one per 32 output rows) use
- * different subsets of the words and may alternate freely on one communicator. */
-constexpr int kTpMaxCtas = 256;
+ *   [ call counter u32, pad to kTpHeaderBytes | slots: [2][tp][max_tokens * hidden] x 8 bytes ]
+ * A slot element is ONE 8-byte word {FP32 partial sum, call number + 1}: the sender writes it with a
+ * single store into every rank's buffer and the receiver polls the word itself until the tag is the
+ * current call's.  Value and "it has arrived" travel in the same transaction, so the exchange needs
+ * no fence, no separate flag and no second trip over NVLink, and the test does not depend on which
+ * kernel served the earlier calls (the single-pass and the batched kernels may alternate freely on
+ * one communicator).  Buffers alternate by call parity: a rank can be at most one call ahead of a
+ * peer, because completing a call needs every peer's words of that call. */
 constexpr int kTpMaxRanks = 16;
-constexpr size_t kTpSeqOffset = (size_t)kTpMaxCtas * kTpMaxRanks * sizeof(unsigned);
-constexpr size_t kTpFlagBytes = kTpSeqOffset + 256;
+constexpr size_t kTpSeqOffset = 0;
+constexpr size_t kTpHeaderBytes = 256;
+constexpr uint32_t kTpPollLimit = 1u << 20; /* polls of one tagged word before a receiver gives up (about a second) */
+
+__device__ __forceinline__ void tp_store_tagged(unsigned long long *p, float v, unsigned tag) {
+    const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+/* true when the word carries `tag`; *v is its value then */
+__device__ __forceinline__ bool tp_load_tagged(const unsigned long long *p, unsigned tag, float *v) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    *v = __uint_as_float((unsigned)w);
+    return (unsigned)(w >> 32) == tag;
+}
 
 /* Tensor-parallel exchange tables (device arrays of per-rank pointers, set up once at load). */
 struct FusedTp {
     int tp, rank;
-    float *const *peer_slots;    /* [tp] -> each rank's [2][tp][slot_stride] fp32 */
-    unsigned *const *peer_flags; /* [tp] -> each rank's arrival words [kTpMaxCtas][kTpMaxRanks] */
-    int slot_stride;             /* floats per (parity, rank) slot */
+    unsigned long long *const *peer_slots; /* [tp] -> each rank's [2][tp][slot_stride] tagged words */
+    int slot_stride;             /* elements per (parity, rank) slot */
     unsigned *seq;               /* this rank's call counter for this communicator (device word) */
-    int max_ctas;                /* grid size every rank uses */
 };
 /* Optional RMSNorm fused into the kernel's input stage (weight == NULL: the input is already normalized). */
 struct FusedNorm {

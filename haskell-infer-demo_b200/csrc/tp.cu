@@ -6,12 +6,12 @@
  * (csrc/collective.cu:108-144, 168-219) for this path: no staging copies, no host-issued adds.
  *
  * One exchange buffer per rank, one allocation:
- *     [ arrival words: kTpMaxCtas x kTpMaxRanks x u32 | call counter u32, pad | slots: 2 x tp x max_tokens*hidden x f32 ]
- * Word [c][r] is the number (+1) of the last call for which rank r's "CTA c" delivered its rows; the
- * kernel compares it with a device-resident call counter, so replaying a captured graph stays
- * correct and kernels with different grids can share the communicator.  Slots are double buffered
- * by call parity: a rank can be at most one call ahead of a peer, because completing a call needs
- * every peer's arrival for that call.
+ *     [ call counter u32, pad | slots: 2 x tp x max_tokens*hidden x {f32 value, u32 call number + 1} ]
+ * Every element travels as one 8-byte store whose upper half names the call it belongs to; the
+ * receiver polls the element itself.  The kernel takes the call number from a device-resident
+ * counter, so replaying a captured graph stays correct.  Slots are double buffered by call parity:
+ * a rank can be at most one call ahead of a peer, because completing a call needs every peer's
+ * elements of that call.
  */
 #include <string.h>
 
@@ -29,24 +29,16 @@ struct TpComm {
     uint8_t *local = nullptr;             /* this rank's exchange buffer */
     uint8_t *peer[kTpMaxRanks] = {};      /* every rank's buffer as seen from this device */
     bool opened[kTpMaxRanks] = {};        /* peer[r] came from cudaIpcOpenMemHandle */
-    float **d_slots = nullptr;            /* device arrays handed to the kernel */
-    unsigned **d_flags = nullptr;
+    unsigned long long **d_slots = nullptr; /* device array handed to the kernel */
     bool connected = false;
 };
 
 static int tp_publish_tables(TpComm *c) {
-    float *slots[kTpMaxRanks];
-    unsigned *flags[kTpMaxRanks];
-    for (int r = 0; r < c->tp; ++r) {
-        flags[r] = (unsigned *)c->peer[r];
-        slots[r] = (float *)(c->peer[r] + kTpFlagBytes);
-    }
+    unsigned long long *slots[kTpMaxRanks];
+    for (int r = 0; r < c->tp; ++r) slots[r] = (unsigned long long *)(c->peer[r] + kTpHeaderBytes);
     if (!c->d_slots && cudaMalloc(&c->d_slots, sizeof(slots)) != cudaSuccess)
         return fail(FFN_ERR_ALLOC, "ffn_tp: cannot allocate the peer table");
-    if (!c->d_flags && cudaMalloc(&c->d_flags, sizeof(flags)) != cudaSuccess)
-        return fail(FFN_ERR_ALLOC, "ffn_tp: cannot allocate the peer table");
     FFN_CUDA_TRY(cudaMemcpy(c->d_slots, slots, sizeof(slots), cudaMemcpyHostToDevice), "ffn_tp: peer table");
-    FFN_CUDA_TRY(cudaMemcpy(c->d_flags, flags, sizeof(flags), cudaMemcpyHostToDevice), "ffn_tp: peer table");
     c->connected = true;
     return FFN_OK;
 }
@@ -68,7 +60,7 @@ int ffn_tp_create(FfnTpComm **out, int tp, int rank, int hidden, int max_tokens)
     if (!c) return fail(FFN_ERR_ALLOC, "ffn_tp_create: out of host memory");
     c->tp = tp; c->rank = rank; c->hidden = hidden; c->max_tokens = max_tokens;
     if (cudaGetDevice(&c->device) != cudaSuccess) { delete c; return fail(FFN_ERR_CUDA, "ffn_tp_create: no CUDA device"); }
-    c->bytes = kTpFlagBytes + (size_t)2 * tp * max_tokens * hidden * sizeof(float);
+    c->bytes = kTpHeaderBytes + (size_t)2 * tp * max_tokens * hidden * sizeof(unsigned long long);
     if (cudaMalloc(&c->local, c->bytes) != cudaSuccess) {
         (void)cudaGetLastError();
         delete c;
@@ -159,7 +151,6 @@ int ffn_tp_destroy(FfnTpComm *comm) {
     for (int r = 0; r < c->tp; ++r)
         if (c->opened[r]) (void)cudaIpcCloseMemHandle(c->peer[r]);
     if (c->d_slots) cudaFree(c->d_slots);
-    if (c->d_flags) cudaFree(c->d_flags);
     if (c->local) cudaFree(c->local);
     delete c;
     (void)cudaGetLastError();
@@ -180,10 +171,9 @@ int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *
     if (I <= 0 || I % FFN_INT4_GROUP) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: the rank's intermediate size %d splits K at a non-group boundary", I);
     FusedTp t;
     t.tp = c->tp; t.rank = c->rank;
-    t.peer_slots = c->d_slots; t.peer_flags = c->d_flags;
+    t.peer_slots = c->d_slots;
     t.slot_stride = c->max_tokens * c->hidden;
     t.seq = (unsigned *)(c->local + kTpSeqOffset);
-    t.max_ctas = kTpMaxCtas;
     uint16_t *act = (uint16_t *)ws + (size_t)tokens * H + (size_t)2 * tokens * I;
     int st = fused_ffn_launch((cudaStream_t)stream, normed, act, layer_out, w, tokens, H, I, &t, residual, nullptr);
     if (st == FFN_NOT_ADMITTED && tokens <= 64) {
@@ -208,8 +198,8 @@ static int decode_layer(TpComm *c, cudaStream_t stream, void *h, void *ws, void 
     FusedTp t = {};
     const FusedTp *tp = nullptr;
     if (c && c->tp > 1) {
-        t.tp = c->tp; t.rank = c->rank; t.peer_slots = c->d_slots; t.peer_flags = c->d_flags;
-        t.slot_stride = c->max_tokens * c->hidden; t.max_ctas = kTpMaxCtas; t.seq = (unsigned *)(c->local + kTpSeqOffset);
+        t.tp = c->tp; t.rank = c->rank; t.peer_slots = c->d_slots;
+        t.slot_stride = c->max_tokens * c->hidden; t.seq = (unsigned *)(c->local + kTpSeqOffset);
         tp = &t;
     }
     uint16_t *normed = (uint16_t *)ws;

@@ -41,3 +41,31 @@ def test_tp_parity_multi_gpu(ranks):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env, cwd=ROOT)
     assert proc.returncode == 0 and "tp_worker ok" in proc.stdout, proc.stdout[-3000:] + proc.stderr[-3000:]
+
+
+@pytest.mark.parametrize("tokens", [1, 8])
+def test_withheld_rank_is_reported_not_waited_for_forever(cuda, tokens):
+    """Failure detection without a GPU fault: rank 0 of a two-rank communicator runs alone (rank 1 is
+    never launched, so its partial sums never arrive).  The kernel's wait for them is bounded (about
+    a second); it must return, the host must see the status naming the wait, and the device must
+    stay usable: the next plain call gives the right answer.  Covers the single-pass kernel and the
+    batched pair."""
+    from oracle import ffn_oracle as o
+    from gpu_util import assert_ffn_close, dev_bf16, host_f32, upload_layer
+    from haskell_infer_demo_b200 import lib as L
+    from haskell_infer_demo_b200.ops import TpComm
+    x, layers = o.draw_config(1024, 3072, 0, tokens=tokens)
+    comms = TpComm.local([cuda, cuda], 1024, 8)      # both ends on this device; only rank 0 is driven
+    try:
+        half = upload_layer(layers[0], cuda, tp=2, rank=0)
+        comms[0].forward_mlp(half, dev_bf16(x, cuda))
+        with pytest.raises(L.FfnError, match="partial sums"):
+            L.device_status()
+        L.device_status()                            # the status was cleared by reading it
+        whole = upload_layer(layers[0], cuda)
+        got = host_f32(whole.forward_mlp_prepared(dev_bf16(x, cuda)))
+        L.device_status()
+        assert_ffn_close(got, o.ffn(layers[0], x), "after a withheld rank")
+    finally:
+        for c in comms:
+            c.close()
