@@ -20,19 +20,25 @@
  * so one 16-byte shared load feeds both MMAs.
  *
  * Two launches per FFN: gate/up + SiLU*up (writes act, natural order for the caller and permuted for
- * the next launch), then down with the cross-rank exchange in its epilogue (same slot / flag protocol
- * as the fused decode kernel: CTA c of every rank owns the same 32 output rows).
+ * the next launch), then down with the cross-rank exchange in its epilogue (the tagged-word protocol
+ * of the fused decode kernel).  A CTA takes 128 weight rows (64 gate + 64 up, or 128 down rows), one
+ * 16-row MMA tile per warp, so every activation byte it brings into shared memory is used by 128
+ * rows.  The down projection has only H/128 row blocks, so its K range is split over several CTAs
+ * per block; each writes FP32 partial sums to global memory and the last one to arrive adds them in
+ * split order (deterministic) and runs the epilogue.
  */
 #include "common.cuh"
 #include "kernels.h"
 
 namespace ffn {
 
-constexpr int kMmaWarps = 4;          /* one 128-wide group of the K chunk each */
+constexpr int kMmaWarps = 8;          /* one 16-row MMA tile each, every group of the K chunk */
 constexpr int kMmaThreads = kMmaWarps * 32;
-constexpr int kMmaRows = 32;          /* weight rows per CTA: two 16-row MMA tiles */
-constexpr int kMmaKC = 512;           /* K per pipeline stage: 4 groups */
-constexpr int kWRowBytes = kMmaKC / 2 + 16;   /* 272: conflict-free 32-bit reads down 8 rows */
+constexpr int kMmaRows = 16 * kMmaWarps; /* 128 weight rows per CTA: the activations a CTA loads are reused 128 times */
+constexpr int kMmaKC = 256;           /* K per pipeline stage: 2 groups */
+constexpr int kMmaGroupsPerChunk = kMmaKC / FFN_INT4_GROUP;
+constexpr int kWRowBytes = kMmaKC / 2 + 16;   /* 144: conflict-free 32-bit reads down 8 rows */
+constexpr int kMmaMaxSplits = 8;      /* K splits of the down projection (partial sums through global memory) */
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
@@ -78,6 +84,10 @@ struct MmaParams {
     uint16_t *act_perm;       /* gate/up: bf16 [M][N] permuted order (input of the down launch) */
     uint16_t *out;            /* down: bf16 [M][N] */
     uint16_t *residual;       /* down: optional bf16 [M][N], h <- bf16(h + y) */
+    /* down: K split over `splits` CTAs per row block */
+    int splits;
+    float *partial;           /* [splits][M][N] fp32 */
+    unsigned *arrivals;       /* [N / kMmaRows], zero between launches */
     /* tensor parallelism (down only) */
     int tp, rank, slot_stride;
     unsigned long long *const *peer_slots;
@@ -85,52 +95,54 @@ struct MmaParams {
     unsigned *status;         /* word 3 of the device's synchronisation words */
 };
 
-/* One CTA: 32 weight rows (two tiles: [gate16 | up16] or down32) x all tokens, K streamed in 512-wide
- * chunks through a cp.async ring; warp ks takes group ks of every chunk for both tiles.  On return
- * red[(ks*32 + row) * ldr + token] holds the warps' FP32 partial sums. */
+/* One CTA: 128 weight rows ([gate64 | up64] or down128) x all tokens over the groups [gbeg, gend) of
+ * K, streamed in 256-wide chunks through a cp.async ring; warp wp owns rows 16*wp .. 16*wp+15.  On
+ * return red[row * ldr + token] holds the FP32 sums. */
 template <int NT, bool PAIRS>
-__device__ __forceinline__ void mma_block(const MmaParams &P, int row0, uint8_t *smem, int stages, float *red, int ldr) {
-    const int tid = threadIdx.x, lane = tid & 31, ks = tid >> 5;
+__device__ __forceinline__ void mma_block(const MmaParams &P, int row0, int gbeg, int gend, uint8_t *smem, int stages,
+                                          float *red, int ldr) {
+    const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int xrow = kMmaKC * 2 + 64;                     /* bytes per token row of a stage, = 64 mod 128 */
-    const int stage_bytes = kMmaRows * kWRowBytes + NT * 8 * xrow;
+    constexpr int xrow = kMmaKC * 2 + 64;                 /* bytes per token row of a stage, = 64 mod 128 */
+    constexpr int stage_bytes = kMmaRows * kWRowBytes + NT * 8 * xrow;
     const int G = P.K / FFN_INT4_GROUP;
-    const int nchunks = (P.K + kMmaKC - 1) / kMmaKC;
+    const int ngroups = gend - gbeg;
+    const int nchunks = (ngroups + kMmaGroupsPerChunk - 1) / kMmaGroupsPerChunk;
     const uint32_t sbase = smem_addr(smem);
 
     auto row_of = [&](int r) -> int { /* global weight row of local row r */
-        return PAIRS ? (r < 16 ? row0 + r : P.up_offset + row0 + (r - 16)) : row0 + r;
+        return PAIRS ? (r < kMmaRows / 2 ? row0 + r : P.up_offset + row0 + (r - kMmaRows / 2)) : row0 + r;
     };
-    /* Each thread copies the same pieces of every chunk: 4 weight pieces (row r = i/16, 16-byte column
-     * c = i%16) and NT*4 activation pieces (token m = i/64, column c = i%64).  Sources and shared
+    /* Each thread copies the same pieces of every chunk: 4 weight pieces (row r = i/8, 16-byte column
+     * c = i%8) and NT activation pieces (token m = i/32, column c = i%32).  Sources and shared
      * offsets are fixed per thread, so a chunk costs one add per piece. */
     const uint8_t *wsrc[4];
     uint32_t wdst[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-        const int i = tid + q * kMmaThreads, r = i >> 4, c = i & 15;
-        wsrc[q] = P.w + (size_t)row_of(r) * (P.K / 2) + c * 16;
+        const int i = tid + q * kMmaThreads, r = i >> 3, c = i & 7;
+        wsrc[q] = P.w + (size_t)row_of(r) * (P.K / 2) + (size_t)gbeg * (FFN_INT4_GROUP / 2) + c * 16;
         wdst[q] = (uint32_t)(r * kWRowBytes + c * 16);
     }
-    const uint16_t *xsrc[NT * 4];
-    uint32_t xdst[NT * 4];
+    const uint16_t *xsrc[NT];
+    uint32_t xdst[NT];
 #pragma unroll
-    for (int q = 0; q < NT * 4; ++q) {
-        const int i = tid + q * kMmaThreads, m = i >> 6, c = i & 63;
-        xsrc[q] = m < P.M ? P.x + (size_t)m * P.K + c * 8 : nullptr;
+    for (int q = 0; q < NT; ++q) {
+        const int i = tid + q * kMmaThreads, m = i >> 5, c = i & 31;
+        xsrc[q] = m < P.M ? P.x + (size_t)m * P.K + (size_t)gbeg * FFN_INT4_GROUP + c * 8 : nullptr;
         xdst[q] = (uint32_t)(kMmaRows * kWRowBytes + m * xrow + c * 16);
     }
-    const int tcol_w = (tid & 15) * 32, tcol_x = (tid & 63) * 8; /* first K index of this thread's pieces */
+    const int tcol_w = (tid & 7) * 32, tcol_x = (tid & 31) * 8; /* first K index (in the chunk) of this thread's pieces */
     auto issue = [&](int chunk) {
         const uint32_t st = sbase + (uint32_t)(chunk % stages) * stage_bytes;
-        const int k0 = chunk * kMmaKC, kc = min(kMmaKC, P.K - k0);
+        const int k0 = chunk * kMmaKC, kc = min(kMmaKC, ngroups * FFN_INT4_GROUP - k0);
         if (tcol_w < kc) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) cp_async16(st + wdst[q], wsrc[q] + k0 / 2);
         }
         if (tcol_x < kc) {
 #pragma unroll
-            for (int q = 0; q < NT * 4; ++q)
+            for (int q = 0; q < NT; ++q)
                 if (xsrc[q]) cp_async16(st + xdst[q], xsrc[q] + k0);
         }
         cp_async_commit();
@@ -143,13 +155,13 @@ __device__ __forceinline__ void mma_block(const MmaParams &P, int row0, uint8_t 
             *(uint4 *)(smem + (size_t)s * stage_bytes + kMmaRows * kWRowBytes + m * xrow + c * 16) = make_uint4(0, 0, 0, 0);
         }
 
-    float acc[2][NT][4];
+    float acc[NT][4];
 #pragma unroll
-    for (int rt = 0; rt < 2; ++rt)
+    for (int n = 0; n < NT; ++n)
 #pragma unroll
-        for (int n = 0; n < NT; ++n)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[rt][n][i] = 0.0f;
+        for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+    const int r_lo = row_of(wp * 16 + g), r_hi = row_of(wp * 16 + g + 8);
+    const uint16_t *s_lo = P.s + (size_t)r_lo * G + gbeg, *s_hi = P.s + (size_t)r_hi * G + gbeg;
 
     for (int c = 0; c < stages - 1; ++c) {
         if (c < nchunks) issue(c); else cp_async_commit();
@@ -159,67 +171,53 @@ __device__ __forceinline__ void mma_block(const MmaParams &P, int row0, uint8_t 
         if (stages == 4) cp_async_wait<2>(); else if (stages == 3) cp_async_wait<1>(); else cp_async_wait<0>();
         __syncthreads(); /* everyone sees chunk c, and everyone is done with the buffer refilled below */
         if (c + stages - 1 < nchunks) issue(c + stages - 1); else cp_async_commit();
-        const int grp = c * (kMmaKC / FFN_INT4_GROUP) + ks; /* this warp's group of the chunk */
-        if (grp < G) {
-            const uint32_t st = sbase + (uint32_t)(c % stages) * stage_bytes;
-            const uint32_t xs = st + kMmaRows * kWRowBytes + (uint32_t)g * xrow + (uint32_t)ks * 256;
-            float sc[2][2];
+        const uint32_t st = sbase + (uint32_t)(c % stages) * stage_bytes;
 #pragma unroll
-            for (int rt = 0; rt < 2; ++rt) {
-                sc[rt][0] = bf16_bits_to_f32(__ldg(P.s + (size_t)row_of(rt * 16 + g) * G + grp));
-                sc[rt][1] = bf16_bits_to_f32(__ldg(P.s + (size_t)row_of(rt * 16 + g + 8) * G + grp));
-            }
-            float part[2][NT][4];
-#pragma unroll
-            for (int rt = 0; rt < 2; ++rt)
+        for (int gi = 0; gi < kMmaGroupsPerChunk; ++gi) {
+            const int grp = c * kMmaGroupsPerChunk + gi; /* relative to gbeg */
+            if (grp < ngroups) {
+                const float sc_lo = bf16_bits_to_f32(__ldg(s_lo + grp)), sc_hi = bf16_bits_to_f32(__ldg(s_hi + grp));
+                const uint32_t xs = st + kMmaRows * kWRowBytes + (uint32_t)g * xrow + (uint32_t)gi * 256;
+                const uint32_t wa0 = st + (uint32_t)(wp * 16 + g) * kWRowBytes + (uint32_t)gi * 64 + (uint32_t)t * 4;
+                float part[NT][4];
 #pragma unroll
                 for (int n = 0; n < NT; ++n)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) part[rt][n][i] = 0.0f;
+                    for (int i = 0; i < 4; ++i) part[n][i] = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint32_t a[2][2][4]; /* [tile][mma of the pair][a0..a3] */
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t a[2][4]; /* [mma of the pair][a0..a3] */
+                    const uint32_t w_lo = lds32(wa0 + (uint32_t)j * 16), w_hi = lds32(wa0 + (uint32_t)j * 16 + 8 * kWRowBytes); /* rows g, g+8 */
+                    a[0][0] = codes_bf16x2(w_lo, 0); a[0][1] = codes_bf16x2(w_hi, 0);
+                    a[0][2] = codes_bf16x2(w_lo, 1); a[0][3] = codes_bf16x2(w_hi, 1);
+                    a[1][0] = codes_bf16x2(w_lo, 2); a[1][1] = codes_bf16x2(w_hi, 2);
+                    a[1][2] = codes_bf16x2(w_lo, 3); a[1][3] = codes_bf16x2(w_hi, 3);
 #pragma unroll
-                for (int rt = 0; rt < 2; ++rt) {
-                    const uint32_t wa = st + (uint32_t)(rt * 16 + g) * kWRowBytes + (uint32_t)ks * 64 + (uint32_t)(4 * j + t) * 4;
-                    const uint32_t w_lo = lds32(wa), w_hi = lds32(wa + 8 * kWRowBytes); /* rows g and g+8 */
-                    a[rt][0][0] = codes_bf16x2(w_lo, 0); a[rt][0][1] = codes_bf16x2(w_hi, 0);
-                    a[rt][0][2] = codes_bf16x2(w_lo, 1); a[rt][0][3] = codes_bf16x2(w_hi, 1);
-                    a[rt][1][0] = codes_bf16x2(w_lo, 2); a[rt][1][1] = codes_bf16x2(w_hi, 2);
-                    a[rt][1][2] = codes_bf16x2(w_lo, 3); a[rt][1][3] = codes_bf16x2(w_hi, 3);
-                }
-#pragma unroll
-                for (int n = 0; n < NT; ++n) {
-                    const uint4 b = lds128(xs + (uint32_t)n * 8 * xrow + (uint32_t)(4 * j + t) * 16);
-#pragma unroll
-                    for (int rt = 0; rt < 2; ++rt) {
-                        mma_bf16(part[rt][n], a[rt][0], b.x, b.y);
-                        mma_bf16(part[rt][n], a[rt][1], b.z, b.w);
+                    for (int n = 0; n < NT; ++n) {
+                        const uint4 b = lds128(xs + (uint32_t)n * 8 * xrow + (uint32_t)(4 * j + t) * 16);
+                        mma_bf16(part[n], a[0], b.x, b.y);
+                        mma_bf16(part[n], a[1], b.z, b.w);
                     }
                 }
-            }
-#pragma unroll
-            for (int rt = 0; rt < 2; ++rt)
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
-                    acc[rt][n][0] = fmaf(part[rt][n][0], sc[rt][0], acc[rt][n][0]);
-                    acc[rt][n][1] = fmaf(part[rt][n][1], sc[rt][0], acc[rt][n][1]);
-                    acc[rt][n][2] = fmaf(part[rt][n][2], sc[rt][1], acc[rt][n][2]);
-                    acc[rt][n][3] = fmaf(part[rt][n][3], sc[rt][1], acc[rt][n][3]);
+                    acc[n][0] = fmaf(part[n][0], sc_lo, acc[n][0]);
+                    acc[n][1] = fmaf(part[n][1], sc_lo, acc[n][1]);
+                    acc[n][2] = fmaf(part[n][2], sc_hi, acc[n][2]);
+                    acc[n][3] = fmaf(part[n][3], sc_hi, acc[n][3]);
                 }
+            }
         }
     }
     cp_async_wait<0>();
     __syncthreads(); /* the ring is dead; `red` may alias it */
 #pragma unroll
-    for (int rt = 0; rt < 2; ++rt)
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-            float *r0 = red + (size_t)(ks * kMmaRows + rt * 16 + g) * ldr + n * 8 + 2 * t;
-            float *r1 = r0 + 8 * ldr;
-            r0[0] = acc[rt][n][0]; r0[1] = acc[rt][n][1];
-            r1[0] = acc[rt][n][2]; r1[1] = acc[rt][n][3];
-        }
+    for (int n = 0; n < NT; ++n) {
+        float *r0 = red + (size_t)(wp * 16 + g) * ldr + n * 8 + 2 * t;
+        float *r1 = r0 + 8 * ldr;
+        r0[0] = acc[n][0]; r0[1] = acc[n][1];
+        r1[0] = acc[n][2]; r1[1] = acc[n][3];
+    }
     __syncthreads();
 }
 
@@ -228,17 +226,13 @@ __global__ void __launch_bounds__(kMmaThreads) gate_up_mma_kernel(const MmaParam
     extern __shared__ __align__(128) uint8_t smem[];
     const int ldr = NT * 8 + 1;
     float *red = (float *)smem;
-    const int row0 = blockIdx.x * 16; /* first gate/up pair of this CTA */
+    constexpr int kPairs = kMmaRows / 2;
+    const int row0 = blockIdx.x * kPairs; /* first gate/up pair of this CTA */
     if (blockIdx.x == 0 && threadIdx.x == 0 && P.tp_seq) atomicAdd(P.tp_seq, 1u); /* the call's number, read by the down launch */
-    mma_block<NT, true>(P, row0, smem, stages, red, ldr);
-    for (int i = threadIdx.x; i < 16 * P.M; i += kMmaThreads) {
-        const int r = i % 16, m = i / 16;
-        float gsum = 0.0f, usum = 0.0f;
-#pragma unroll
-        for (int ks = 0; ks < kMmaWarps; ++ks) {
-            gsum += red[(size_t)(ks * kMmaRows + r) * ldr + m];
-            usum += red[(size_t)(ks * kMmaRows + 16 + r) * ldr + m];
-        }
+    mma_block<NT, true>(P, row0, 0, P.K / FFN_INT4_GROUP, smem, stages, red, ldr);
+    for (int i = threadIdx.x; i < kPairs * P.M; i += kMmaThreads) {
+        const int r = i % kPairs, m = i / kPairs;
+        const float gsum = red[(size_t)r * ldr + m], usum = red[(size_t)(kPairs + r) * ldr + m];
         const uint16_t a = f32_to_bf16_bits(silu_mul(round_bf16(gsum), round_bf16(usum)));
         const int p = row0 + r;
         P.act[(size_t)m * P.up_offset + p] = a;
@@ -249,17 +243,43 @@ __global__ void __launch_bounds__(kMmaThreads) gate_up_mma_kernel(const MmaParam
 template <int NT>
 __global__ void __launch_bounds__(kMmaThreads) down_mma_kernel(const MmaParams P, int stages) {
     extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int last_arrival;
     const int ldr = NT * 8 + 1;
     float *red = (float *)smem;
-    const int row0 = blockIdx.x * kMmaRows;
-    mma_block<NT, false>(P, row0, smem, stages, red, ldr);
+    const int rb = blockIdx.x / P.splits, sp = blockIdx.x % P.splits;
+    const int row0 = rb * kMmaRows;
+    const int G = P.K / FFN_INT4_GROUP;
+    mma_block<NT, false>(P, row0, (int)((long long)G * sp / P.splits), (int)((long long)G * (sp + 1) / P.splits), smem, stages, red, ldr);
+    if (P.splits > 1) {
+        /* this CTA's share of K is done: leave it in global memory; whoever arrives last at the row
+         * block adds the shares in split order and carries on alone */
+        for (int i = threadIdx.x; i < kMmaRows * P.M; i += kMmaThreads) {
+            const int r = i % kMmaRows, m = i / kMmaRows;
+            __stcg(P.partial + ((size_t)sp * P.M + m) * P.N + row0 + r, red[(size_t)r * ldr + m]);
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned before = atomicAdd(P.arrivals + rb, 1u);
+            last_arrival = before == (unsigned)P.splits - 1u;
+            if (last_arrival) P.arrivals[rb] = 0u; /* ready for the next launch */
+        }
+        __syncthreads();
+        if (!last_arrival) return;
+        __threadfence();
+        for (int i = threadIdx.x; i < kMmaRows * P.M; i += kMmaThreads) {
+            const int r = i % kMmaRows, m = i / kMmaRows;
+            float y = 0.0f;
+            for (int q = 0; q < P.splits; ++q) y += __ldcg(P.partial + ((size_t)q * P.M + m) * P.N + row0 + r);
+            red[(size_t)r * ldr + m] = y;
+        }
+        /* each thread reads back only what it wrote to `red` itself: no barrier needed */
+    }
     const unsigned seq = P.tp > 1 ? (*(volatile unsigned *)P.tp_seq - 1u) : 0u;
     const size_t slot = (size_t)((seq & 1u) * P.tp + P.rank) * P.slot_stride;
     for (int i = threadIdx.x; i < kMmaRows * P.M; i += kMmaThreads) {
         const int r = i % kMmaRows, m = i / kMmaRows;
-        float y = 0.0f;
-#pragma unroll
-        for (int ks = 0; ks < kMmaWarps; ++ks) y += red[(size_t)(ks * kMmaRows + r) * ldr + m];
+        const float y = red[(size_t)r * ldr + m];
         const size_t o = (size_t)m * P.N + row0 + r;
         if (P.tp > 1) {
             for (int q = 0; q < P.tp; ++q) tp_store_tagged(P.peer_slots[q] + slot + o, y, seq + 1u);
@@ -312,55 +332,75 @@ __global__ void permute8_kernel(uint16_t *__restrict__ xp, const uint16_t *__res
 }
 
 /* ---- host ----------------------------------------------------------------------------------- */
-static int mma_smem(int nt, int stages, int *stage_bytes_out) {
-    const int xrow = kMmaKC * 2 + 64;
-    const int stage = kMmaRows * kWRowBytes + nt * 8 * xrow;
-    *stage_bytes_out = stage;
-    const int red = kMmaWarps * kMmaRows * (nt * 8 + 1) * (int)sizeof(float);
-    return max(stage * stages, red);
+static int mma_stage_bytes(int nt) { return kMmaRows * kWRowBytes + nt * 8 * (kMmaKC * 2 + 64); }
+static int mma_smem(int nt, int stages) {
+    const int red = kMmaRows * (nt * 8 + 1) * (int)sizeof(float);
+    return max(mma_stage_bytes(nt) * stages, red);
 }
 
+/* Per device: the permuted copies of the input and of act (bf16 [tokens][H + I]), the split-K partial
+ * sums of the down projection and its arrival counters.  Grown on demand, so the first call of a new
+ * size allocates (make it before capturing a graph). */
+struct MmaScratch {
+    uint8_t *base = nullptr;
+    size_t bytes = 0;
+};
+static MmaScratch g_mma_scratch[64];
+
 template <int NT>
-static int launch_pair(const MmaParams &A, const MmaParams &B, int smem_optin, cudaStream_t stream) {
-    int stage = 0;
+static int launch_pair(MmaParams &A, MmaParams &B, int smem_optin, int sm_count, cudaStream_t stream) {
+    /* four stages when two CTAs still fit on an SM, else three if that makes two fit, else four */
     int stages = 4;
-    while (stages > 2 && mma_smem(NT, stages, &stage) > smem_optin) --stages;
-    const int smem = mma_smem(NT, stages, &stage);
+    if (2 * (mma_smem(NT, 4) + 1024) > smem_optin && 2 * (mma_smem(NT, 3) + 1024) <= smem_optin) stages = 3;
+    while (stages > 2 && mma_smem(NT, stages) > smem_optin) --stages;
+    const int smem = mma_smem(NT, stages);
     if (smem > smem_optin) return fail(FFN_ERR_CONFIG, "batched INT4 FFN: %d tokens do not fit shared memory", NT * 8);
+    const int per_sm = 2 * (smem + 1024) <= smem_optin ? 2 : 1;
+    /* K splits of the down projection: fill the CTA slots of the device as evenly as possible */
+    const int blocks = B.N / kMmaRows, slots = sm_count * per_sm, G = B.K / FFN_INT4_GROUP;
+    int best = 1;
+    double best_eff = 0.0;
+    for (int sp = 1; sp <= kMmaMaxSplits && sp * 2 <= max(G, 2); ++sp) {
+        const int units = blocks * sp;
+        const double eff = (double)units / (double)(((units + slots - 1) / slots) * slots);
+        if (eff > best_eff + 1e-9) { best_eff = eff; best = sp; }
+    }
+    B.splits = best;
     FFN_CUDA_TRY(cudaFuncSetAttribute(gate_up_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gate/up MMA: shared-memory opt-in");
     FFN_CUDA_TRY(cudaFuncSetAttribute(down_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "down MMA: shared-memory opt-in");
-    gate_up_mma_kernel<NT><<<A.up_offset / 16, kMmaThreads, smem, stream>>>(A, stages);
+    gate_up_mma_kernel<NT><<<A.up_offset / (kMmaRows / 2), kMmaThreads, smem, stream>>>(A, stages);
     FFN_CUDA_TRY(cudaGetLastError(), "gate/up MMA launch");
-    down_mma_kernel<NT><<<B.N / kMmaRows, kMmaThreads, smem, stream>>>(B, stages);
+    down_mma_kernel<NT><<<blocks * B.splits, kMmaThreads, smem, stream>>>(B, stages);
     FFN_CUDA_TRY(cudaGetLastError(), "down MMA launch");
     return FFN_OK;
 }
-
-/* Per device: room for the permuted copies of the input and of act (bf16 [tokens][H + I]).  Grown on
- * demand, so the first call of a new size allocates (make it before capturing a graph). */
-static void *g_mma_scratch[64];
-static size_t g_mma_scratch_bytes[64];
 
 /* normed bf16 [tokens][H] -> layer_out bf16 [tokens][H]; `act` receives act in natural order. */
 int mma_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                    const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual, unsigned *status) {
     if (tokens < 1 || tokens > 64) return FFN_NOT_ADMITTED;
-    if (H % kMmaRows || I % 16) return FFN_NOT_ADMITTED;
+    if (H % kMmaRows || I % (kMmaRows / 2)) return FFN_NOT_ADMITTED;
     if (((uintptr_t)w->gate_up_i4 & 15) || ((uintptr_t)w->down_i4 & 15) || ((uintptr_t)normed & 15))
         return FFN_NOT_ADMITTED;
-    int dev = 0, smem_optin = 0;
+    int dev = 0, smem_optin = 0, sm_count = 0;
     FFN_CUDA_TRY(cudaGetDevice(&dev), "cudaGetDevice");
     if (dev < 0 || dev >= 64) return fail(FFN_ERR_CONFIG, "device index %d out of range", dev);
     FFN_CUDA_TRY(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev), "smem opt-in");
-    const size_t need = (size_t)tokens * (H + I) * sizeof(uint16_t);
-    if (g_mma_scratch_bytes[dev] < need) {
-        const size_t want = (size_t)64 * (H + I) * sizeof(uint16_t); /* the largest batch this path takes */
-        if (g_mma_scratch[dev]) { FFN_CUDA_TRY(cudaDeviceSynchronize(), "batched INT4 FFN: scratch regrow"); cudaFree(g_mma_scratch[dev]); }
-        g_mma_scratch[dev] = nullptr; g_mma_scratch_bytes[dev] = 0;
-        if (cudaMalloc(&g_mma_scratch[dev], want) != cudaSuccess) { (void)cudaGetLastError(); return fail(FFN_ERR_ALLOC, "batched INT4 FFN: cannot allocate %zu bytes of scratch", want); }
-        g_mma_scratch_bytes[dev] = want;
+    FFN_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev), "SM count");
+    /* layout: [arrival counters 4 KiB | x permuted | act permuted | partial sums], sized for 64 tokens */
+    const size_t counters = 4096;
+    if ((size_t)(H / kMmaRows) * sizeof(unsigned) > counters) return FFN_NOT_ADMITTED;
+    const size_t perm_bytes = ((size_t)64 * (H + I) * sizeof(uint16_t) + 255) / 256 * 256;
+    const size_t want = counters + perm_bytes + (size_t)kMmaMaxSplits * 64 * H * sizeof(float);
+    MmaScratch &sc = g_mma_scratch[dev];
+    if (sc.bytes < want) {
+        if (sc.base) { FFN_CUDA_TRY(cudaDeviceSynchronize(), "batched INT4 FFN: scratch regrow"); cudaFree(sc.base); }
+        sc.base = nullptr; sc.bytes = 0;
+        if (cudaMalloc(&sc.base, want) != cudaSuccess) { (void)cudaGetLastError(); return fail(FFN_ERR_ALLOC, "batched INT4 FFN: cannot allocate %zu bytes of scratch", want); }
+        FFN_CUDA_TRY(cudaMemset(sc.base, 0, counters), "batched INT4 FFN: clear arrival counters");
+        sc.bytes = want;
     }
-    uint16_t *xp = (uint16_t *)g_mma_scratch[dev];
+    uint16_t *xp = (uint16_t *)(sc.base + counters);
     uint16_t *act_perm = xp + (size_t)tokens * H;
     const size_t runs = (size_t)tokens * H / 8;
     permute8_kernel<<<(unsigned)((runs + 255) / 256), 256, 0, stream>>>(xp, (const uint16_t *)normed, runs);
@@ -370,22 +410,24 @@ int mma_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *lay
     A.x = xp; A.w = w->gate_up_i4; A.s = (const uint16_t *)w->gate_up_i4_scales;
     A.M = tokens; A.N = 2 * I; A.K = H; A.up_offset = I;
     A.act = (uint16_t *)act; A.act_perm = act_perm;
-    A.tp = 1; A.status = status;
+    A.tp = 1; A.status = status; A.splits = 1;
     MmaParams B = {};
     B.x = act_perm; B.w = w->down_i4; B.s = (const uint16_t *)w->down_i4_scales;
     B.M = tokens; B.N = H; B.K = I; B.up_offset = 0;
     B.out = (uint16_t *)layer_out; B.residual = (uint16_t *)residual;
-    B.tp = 1; B.status = status;
+    B.tp = 1; B.status = status; B.splits = 1;
+    B.partial = (float *)(sc.base + counters + perm_bytes);
+    B.arrivals = (unsigned *)sc.base;
     if (tp && tp->tp > 1) {
         if (tokens * H > tp->slot_stride) return fail(FFN_ERR_CONFIG, "batched INT4 FFN: %d tokens exceed the exchange buffer", tokens);
         A.tp_seq = tp->seq;
         B.tp = tp->tp; B.rank = tp->rank; B.slot_stride = tp->slot_stride;
         B.peer_slots = tp->peer_slots; B.tp_seq = tp->seq;
     }
-    if (tokens <= 8) return launch_pair<1>(A, B, smem_optin, stream);
-    if (tokens <= 16) return launch_pair<2>(A, B, smem_optin, stream);
-    if (tokens <= 32) return launch_pair<4>(A, B, smem_optin, stream);
-    return launch_pair<8>(A, B, smem_optin, stream);
+    if (tokens <= 8) return launch_pair<1>(A, B, smem_optin, sm_count, stream);
+    if (tokens <= 16) return launch_pair<2>(A, B, smem_optin, sm_count, stream);
+    if (tokens <= 32) return launch_pair<4>(A, B, smem_optin, sm_count, stream);
+    return launch_pair<8>(A, B, smem_optin, sm_count, stream);
 }
 
 }  // namespace ffn
