@@ -38,7 +38,7 @@ L2_BYTES = 126 * 1024 * 1024
 METRIC = "int4_ffn_decode_us_per_step"
 # dram__bytes_read.sum + dram__bytes_write.sum of one fused launch at H=5120, I=17408, M=1, TP=1 (ncu --set
 # full capture summarised in profiles/ffn_fused_kernel_cfg2_tp1.md); other shapes have no capture yet.
-TRAFFIC_BYTES = {(1, 1): 142.26e6}
+TRAFFIC_BYTES = {(1, 1): 144.94e6}
 
 
 def algorithmic_bytes(h, i, tp):

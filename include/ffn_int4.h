@@ -185,9 +185,9 @@ int ffn_forward_mlp_prepared_noalloc(void *stream, const void *normed, void *lay
 typedef struct FfnTpComm FfnTpComm;
 #define FFN_TP_HANDLE_BYTES 64
 
-/* Allocates this rank's exchange buffer on the current device (flags + 2*tp*max_tokens*hidden FP32
- * slots, zeroed).  One communicator per rank; rank order is device-list order as in the reference
- * (csrc/engine.cu:997-1011). */
+/* Allocates this rank's exchange buffer on the current device (a call counter + 2*tp*max_tokens*hidden
+ * 8-byte slots {FP32 partial sum, call number}, zeroed).  One communicator per rank; rank order is
+ * device-list order as in the reference (csrc/engine.cu:997-1011). */
 int ffn_tp_create(FfnTpComm **out, int tp, int rank, int hidden, int max_tokens);
 /* One process per rank: export this rank's buffer (FFN_TP_HANDLE_BYTES bytes), exchange the handles
  * by any host channel, then connect with all tp handles in rank order (own entry ignored). */
@@ -204,9 +204,10 @@ int ffn_tp_destroy(FfnTpComm *comm);
  * (gate/up [2*I/R][H], down [H][I/R], intermediate_size = I/R) exactly as the reference's per-rank
  * MlpWeights do.  `ws` as for ffn_forward_mlp.  If `residual` is non-NULL the kernel also applies
  * residual = bf16(f32(residual) + f32(layer_out)) (residual_add_device, csrc/engine.cu:1428-1433).
- * Every rank must make the same sequence of calls; a rank that never launches makes the others
- * return after a bounded wait with a status ffn_int4_device_status reports.  Token counts the fused
- * kernel does not take (currently > 2) are refused with FFN_ERR_CONFIG. */
+ * Every rank must make the same sequence of calls, each within about a second of the others; a rank
+ * that never launches makes the others return after that bounded wait with a status
+ * ffn_int4_device_status reports.  1 or 2 tokens run the single-launch kernel, 3..64 the tensor-core
+ * pair (exchange in the down launch's epilogue); more are refused with FFN_ERR_CONFIG. */
 int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *ws, void *layer_out,
                        const FfnMlpWeights *w, int tokens, const FfnModelDims *dims, void *residual);
 
