@@ -48,7 +48,8 @@ constexpr int kConsumerThreads = kConsumerWarps * 32;  /* 544 = 17 * 32: I = 174
 constexpr int kThreads = (kConsumerWarps + 2) * 32;    /* 608 */
 constexpr int kMaxStages = 8;
 constexpr int kPartSlots = 4;
-constexpr int kPartFloats = 160;                       /* floats per partial slot: JT*NVROW*RG*CT/16 <= 4*544/16 = 136 */
+constexpr int kPartFloats1 = 160;                      /* floats per partial slot, one token: JT*NVROW*RG*CT/16 <= 4*544/16 = 136 */
+constexpr int kPartFloats2 = 288;                      /* two tokens: <= 8*544/16 = 272 */
 constexpr int kMaxJT = 4;                              /* row steps per thread per tile */
 constexpr uint32_t kSpinLimit = 1u << 22;              /* bounded waits: polls of >= 32..100 ns, i.e. 0.15 .. 0.5 s */
 
@@ -300,6 +301,8 @@ __device__ __forceinline__ float halfwarp_reduce(float (&v)[NV], int lane, unsig
     return r;
 }
 
+struct Smem;
+__host__ __device__ constexpr size_t fused_smem_header(int tokens); /* bytes before the activation copy */
 struct Smem {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
@@ -309,8 +312,12 @@ struct Smem {
     int abort_flag;
     int pad[11];
     float norm_red[2][kConsumerWarps + 3];
-    float part[kPartSlots][kPartFloats];
+    float part[1]; /* kPartSlots slots of kPartFloats1 or kPartFloats2 floats follow (sized by the token count) */
 };
+
+__host__ __device__ constexpr size_t fused_smem_header(int tokens) {
+    return (sizeof(Smem) + (size_t)kPartSlots * (tokens == 1 ? kPartFloats1 : kPartFloats2) * sizeof(float) + 127) / 128 * 128;
+}
 
 __device__ __forceinline__ void give_up(Smem *sm, unsigned *sync, int where) {
     sm->abort_flag = 1;
@@ -331,7 +338,8 @@ template <int CIT, int MT, bool PAIRS>
 __device__ __forceinline__ void consume_phase(const FusedParams &P, const PhasePlan &pl, Smem *sm,
                                               const uint16_t *xs, uint8_t *ring, int tile0) {
     constexpr int NVROW = (PAIRS ? 2 : 1) * MT;
-    constexpr int JTM = 4 / NVROW; /* row steps per thread per tile: four values per reduction */
+    constexpr int VALS = 4 * MT;   /* values a thread carries through a tile: one transposed reduction per four */
+    constexpr int JTM = VALS / NVROW; /* row steps per thread per tile: 2 of pairs, 4 of single rows */
     const int stage_bytes = P.stage_bytes, nstages = P.nstages;
     const uint32_t ring_addr = smem_u32(ring);
     const int ti = threadIdx.x - 32;
@@ -427,11 +435,13 @@ __device__ __forceinline__ void consume_phase(const FusedParams &P, const PhaseP
                 return;
             }
         }
-        float *part = sm->part[pslot];
+        float *part = sm->part + (size_t)pslot * (MT == 1 ? kPartFloats1 : kPartFloats2);
 
         /* all row steps of the tile first, then ONE transposed half-warp reduction of up to four
          * values (row step x gate/up x token) instead of one reduction per row */
-        float val[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float val[VALS];
+#pragma unroll
+        for (int v = 0; v < VALS; ++v) val[v] = 0.0f;
         if (active && !(P.debug & 1)) {
             /* No data-dependent branches in here: a column chunk past the row end reads a clamped
              * address against an all-zero prepared slice, a row past the tile end reads the tile's
@@ -474,11 +484,15 @@ __device__ __forceinline__ void consume_phase(const FusedParams &P, const PhaseP
                 }
             }
             /* whole half-warps are active or not (CT is a multiple of 16) */
-            const float r = halfwarp_reduce<4>(val, lane, hmask);
             const int l16 = lane & 15;
-            if ((l16 & 3) == 0) {
-                const int v = l16 >> 2, j = v / NVROW, i = v % NVROW, p = rg + j * pl.RG;
-                if (j < pl.JT && p < rows) part[((size_t)p * NVROW + i) * pl.nhw + (ct >> 4)] = r;
+#pragma unroll
+            for (int q = 0; q < VALS / 4; ++q) {
+                float four[4] = {val[4 * q], val[4 * q + 1], val[4 * q + 2], val[4 * q + 3]};
+                const float r = halfwarp_reduce<4>(four, lane, hmask);
+                if ((l16 & 3) == 0) {
+                    const int v = 4 * q + (l16 >> 2), j = v / NVROW, i = v % NVROW, p = rg + j * pl.RG;
+                    if (j < pl.JT && p < rows) part[((size_t)p * NVROW + i) * pl.nhw + (ct >> 4)] = r;
+                }
             }
         }
         __syncwarp();
@@ -506,7 +520,7 @@ __device__ __forceinline__ bool epilogue_phase(const FusedParams &P, const Phase
             give_up(sm, P.sync, ST_PART_FULL);
             return false;
         }
-        const float *part = sm->part[pslot];
+        const float *part = sm->part + (size_t)pslot * (MT == 1 ? kPartFloats1 : kPartFloats2);
         for (int i = lane; i < rows * MT; i += 32) {
             const int p = i / MT, m = i % MT;
             const int row = row_begin + lt * pl.TR + p;
@@ -542,7 +556,7 @@ template <int CIT1, int CIT2, int MT>
 __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParams P) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Smem *sm = (Smem *)smem_raw;
-    uint16_t *xs = (uint16_t *)(smem_raw + ((sizeof(Smem) + 127) / 128) * 128);
+    uint16_t *xs = (uint16_t *)(smem_raw + fused_smem_header(MT));
     uint8_t *ring = (uint8_t *)xs + P.xs_bytes;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ns = P.nstages;
@@ -763,9 +777,9 @@ static bool plan_phase(PhasePlan &pl, int K, int MT, bool pairs, int target_byte
     pl.RG = kConsumerThreads / pl.CT;
     if (pairs) {
         pl.RG = min(pl.RG, max(1, target_bytes / (2 * pl.rb)));
-        pl.JT = max(1, min(2 / MT, target_bytes / (2 * pl.RG * pl.rb)));
+        pl.JT = max(1, min(2, target_bytes / (2 * pl.RG * pl.rb)));
     } else {
-        pl.JT = max(1, min(kMaxJT / MT, target_bytes / (pl.RG * pl.rb)));
+        pl.JT = max(1, min(kMaxJT, target_bytes / (pl.RG * pl.rb)));
     }
     pl.TR = pl.JT * pl.RG;
     pl.nhw = pl.CT / 16;
@@ -828,7 +842,7 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
     P.p1.rows_total = I; P.p1.up_offset = I;
     P.p2.w = w->down_i4; P.p2.s = (const uint16_t *)w->down_i4_scales;
     P.p2.rows_total = H; P.p2.up_offset = 0;
-    if (P.p1.TR * 2 * tokens * P.p1.nhw > kPartFloats || P.p2.TR * tokens * P.p2.nhw > kPartFloats)
+    if (P.p1.TR * 2 * tokens * P.p1.nhw > (tokens == 1 ? kPartFloats1 : kPartFloats2) || P.p2.TR * tokens * P.p2.nhw > (tokens == 1 ? kPartFloats1 : kPartFloats2))
         return FFN_NOT_ADMITTED;
     if (((uintptr_t)w->gate_up_i4_scales & 15) || ((uintptr_t)w->down_i4_scales & 15)) return FFN_NOT_ADMITTED;
     P.stage_w_bytes = round_up(max(2 * P.p1.TR * P.p1.rb, P.p2.TR * P.p2.rb), 128);
@@ -838,7 +852,7 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
     P.trace = g_trace;
     static const int debug_flags = getenv("FFN_INT4_DEBUG") ? atoi(getenv("FFN_INT4_DEBUG")) : 0;
     P.debug = debug_flags;
-    const size_t fixed = ((sizeof(Smem) + 127) / 128) * 128 + (size_t)P.xs_bytes;
+    const size_t fixed = fused_smem_header(tokens) + (size_t)P.xs_bytes;
     if (fixed + 2 * (size_t)P.stage_bytes > (size_t)d.smem_optin) return FFN_NOT_ADMITTED;
     P.nstages = (int)min((size_t)kMaxStages, ((size_t)d.smem_optin - fixed) / (size_t)P.stage_bytes);
     if (P.nstages < 2) return FFN_NOT_ADMITTED;
@@ -942,8 +956,8 @@ int fused_ffn_launch_noalloc(cudaStream_t stream, const void *normed, void *laye
     P.sc_half_bytes = round_up(max(P.p1.TR * P.p1.G * 2, P.p2.TR * P.p2.G * 2) + 32, 16);
     P.stage_bytes = round_up(P.stage_w_bytes + 2 * P.sc_half_bytes, 128);
     P.xs_bytes = round_up(tokens * I * 2, 128); /* act only: x is read from global memory */
-    const size_t fixed = ((sizeof(Smem) + 127) / 128) * 128 + (size_t)P.xs_bytes;
-    if (P.p1.TR * 2 * tokens * P.p1.nhw > kPartFloats || P.p2.TR * tokens * P.p2.nhw > kPartFloats ||
+    const size_t fixed = fused_smem_header(tokens) + (size_t)P.xs_bytes;
+    if (P.p1.TR * 2 * tokens * P.p1.nhw > (tokens == 1 ? kPartFloats1 : kPartFloats2) || P.p2.TR * tokens * P.p2.nhw > (tokens == 1 ? kPartFloats1 : kPartFloats2) ||
         fixed + 2 * (size_t)P.stage_bytes > (size_t)d.smem_optin)
         return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: the shape does not fit shared memory");
     P.nstages = (int)min((size_t)kMaxStages, ((size_t)d.smem_optin - fixed) / (size_t)P.stage_bytes);
