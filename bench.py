@@ -164,7 +164,10 @@ def run_ours(args):
         g.manual_seed(99)
         layers = [DenseMlp(*lay.tensors[:4], post_norm_w=(_t.randn(h, generator=g, device=dev) * 0.1).to(_t.bfloat16))
                   for lay in layers]
-    comm = TpComm.over_process_group(h, max(m, 2)) if world > 1 else None
+    use_nccl = world > 1 and args.exchange == "nccl"
+    if use_nccl and args.layers > 0:
+        raise SystemExit("--exchange nccl is a single-layer comparison; drop --layers")
+    comm = TpComm.over_process_group(h, max(m, 2)) if world > 1 and not use_nccl else None
     nl = max(args.layers, 1)
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234)
@@ -182,6 +185,8 @@ def run_ours(args):
         lay = layers[k % copies]
         if comm is None:
             lay.forward_mlp_prepared(x, ws=ws, layer_out=out)
+            if use_nccl:
+                dist.all_reduce(out)
         else:
             comm.forward_mlp(lay, x, ws=ws, layer_out=out)
 
@@ -236,6 +241,8 @@ def run_ours(args):
             y_host.copy_(x_dev, non_blocking=True)
         elif comm is None:
             lay.forward_mlp_prepared(x_dev, ws=ws, layer_out=out)
+            if use_nccl:
+                dist.all_reduce(out)
             y_host.copy_(out, non_blocking=True)
         else:
             comm.forward_mlp(lay, x_dev, ws=ws, layer_out=out)
@@ -278,7 +285,9 @@ def run_ours(args):
                          "algorithmic_bytes_per_launch": per_rank_bytes, "launches_per_step": nl},
             "e2e": {"value": round(e2e_us, 3), "unit": "us/step", "h2d_bytes_per_step": m * h * 2,
                     "d2h_bytes_per_step": m * h * 2},
-            "gpu_launches": args.steps * nl * (1 if m <= 2 else 4),
+            "gpu_launches": args.steps * nl * (1 if m <= 2 else (4 if args.layers else 3)),
+            "exchange": ("none (one GPU)" if world == 1 else "in-kernel tagged-word exchange over NVLink peer memory"
+                         if not use_nccl else "comparison variant: NCCL all-reduce of the BF16 output after the kernel"),
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu and not args.layers:
@@ -381,6 +390,10 @@ def main():
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="N > 1 only. fused: the cross-rank sum inside the FFN kernel (the product). nccl: comparison "
+                         "variant - the same kernel per rank without an exchange, then an NCCL all-reduce of the BF16 "
+                         "[M,H] output, which is what the reference's leader all-reduce computes")
     ap.add_argument("--layers", type=int, default=0,
                     help="0: one FFN per step (the headline workload).  L > 0: a step is one pass of h <- h + "
                          "FFN_l(RMSNorm_l(h)) through L independent layers (BASELINE configs[4] at L=64)")

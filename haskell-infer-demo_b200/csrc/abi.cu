@@ -189,6 +189,26 @@ int ffn_gemma_rms_norm(void *out, const void *x, const void *weight, int cols, i
     return gemma_rms_norm(out, x, weight, cols, rows, eps, 1, (cudaStream_t)stream);
 }
 
+int ffn_residual_norm(void *normed, void *residual, const void *sublayer, const void *weight, int hidden, int rows,
+                      float eps, int gemma, void *stream) {
+    clear_error();
+    if (hidden <= 0 || rows < 0 || !(eps > 0.0f) || !(eps < 3.0e38f))
+        return fail(FFN_ERR_CONFIG, "ffn_residual_norm: invalid shape or epsilon");
+    if (rows == 0) return FFN_OK;
+    if (!normed || !residual || !sublayer || !weight) return fail(FFN_ERR_CONFIG, "ffn_residual_norm: null buffer");
+    return residual_norm(normed, residual, sublayer, weight, hidden, rows, eps, gemma ? 1 : 0, (cudaStream_t)stream);
+}
+
+int ffn_silu_mul(void *out, const void *gate, int n, void *stream) {
+    clear_error();
+    if (n < 0) return fail(FFN_ERR_CONFIG, "ffn_silu_mul: negative element count");
+    if (n == 0) return FFN_OK;
+    if (!out || !gate) return fail(FFN_ERR_CONFIG, "ffn_silu_mul: expected contiguous [gate[n], up[n]] input");
+    if (n >= 8 && (n % 8 != 0 || ((uintptr_t)gate & 15) || ((uintptr_t)out & 15)))
+        return fail(FFN_ERR_CONFIG, "ffn_silu_mul: vectorized input/output must be 16-byte aligned and n divisible by 8");
+    return silu_mul_pair(out, gate, n, (cudaStream_t)stream);
+}
+
 int ffn_residual_add(void *dst, const void *src, int n, void *stream) {
     clear_error();
     if (n < 0) return fail(FFN_ERR_CONFIG, "ffn_residual_add: negative element count");
@@ -283,6 +303,40 @@ int test_silu_mul_packed(void *out, const void *packed, int tokens, int intermed
     const cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return (int)e;
     return so.finish() ? -1 : 0;
+}
+
+int test_silu_mul(void *out, const void *gate, int n) {
+    clear_error();
+    if (n < 0) { fprintf(stderr, "test_silu_mul: negative element count\n"); return -1; }
+    if (n == 0) return 0;
+    Staged so, sg;
+    int st = so.acquire(out, (size_t)n * 2, true);
+    if (!st) st = sg.acquire(gate, (size_t)n * 4, false);
+    if (!st) st = ffn_silu_mul(so.dev, sg.dev, n, nullptr);
+    if (st) { fprintf(stderr, "test_silu_mul: %s\n", g_error); return -1; }
+    const cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e;
+    return so.finish() ? -1 : 0;
+}
+
+int test_residual_norm(void *normed, void *residual, const void *sublayer, const void *weight, int hidden, int rows,
+                       float eps, int gemma) {
+    clear_error();
+    if (hidden <= 0 || rows < 0) { fprintf(stderr, "test_residual_norm: invalid shape or epsilon\n"); return -1; }
+    if (rows == 0) return 0;
+    if (!normed || !residual || !sublayer || !weight) { fprintf(stderr, "test_residual_norm: null buffer\n"); return -1; }
+    const size_t bytes = (size_t)rows * hidden * 2;
+    Staged sn, sr, ss, sw;
+    int st = sn.acquire(normed, bytes, true);
+    if (!st) st = sr.acquire(residual, bytes, false);
+    if (!st) st = ss.acquire(sublayer, bytes, false);
+    if (!st) st = sw.acquire(weight, (size_t)hidden * 2, false);
+    sr.writeback = sr.owned; /* the residual is both input and output */
+    if (!st) st = ffn_residual_norm(sn.dev, sr.dev, ss.dev, sw.dev, hidden, rows, eps, gemma, nullptr);
+    if (st) { fprintf(stderr, "test_residual_norm: %s\n", g_error); return -1; }
+    const cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e;
+    return (sn.finish() || sr.finish()) ? -1 : 0;
 }
 
 int test_norm(void *out, const void *x, const void *weight, int rows, int cols) {

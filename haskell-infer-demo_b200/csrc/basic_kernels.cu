@@ -193,6 +193,80 @@ gemma_rms_norm_kernel(uint16_t *__restrict__ out, const uint16_t *__restrict__ x
     }
 }
 
+/* ------------------------------------------------------------------------------------------- */
+/* Residual update + norm in one pass (replaces kernel_residual_norm,                            */
+/* csrc/kernels/flashinfer_norm.cu:112-174): r = bf16(r + sublayer) is stored, and the norm reads */
+/* the ROUNDED r, as the next sublayer will.  The row stays in registers between the passes.      */
+/* ------------------------------------------------------------------------------------------- */
+constexpr int kResNormPerThread = 32; /* 256 threads x 32 elements: rows of up to 8192 stay in registers */
+__global__ void __launch_bounds__(256)
+residual_norm_kernel(uint16_t *__restrict__ normed, uint16_t *__restrict__ residual,
+                     const uint16_t *__restrict__ sublayer, const uint16_t *__restrict__ w, int cols, float eps, int gemma) {
+    __shared__ float red[8];
+    const size_t base = (size_t)blockIdx.x * cols;
+    const bool in_regs = cols <= 256 * kResNormPerThread;
+    float keep[kResNormPerThread];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kResNormPerThread; ++j) {
+        const int i = threadIdx.x + j * 256;
+        keep[j] = 0.0f;
+        if (in_regs && i < cols) {
+            const uint16_t r = f32_to_bf16_bits(bf16_bits_to_f32(residual[base + i]) + bf16_bits_to_f32(sublayer[base + i]));
+            residual[base + i] = r;
+            keep[j] = bf16_bits_to_f32(r);
+            ss = fmaf(keep[j], keep[j], ss);
+        }
+    }
+    if (!in_regs)
+        for (int i = threadIdx.x; i < cols; i += 256) {
+            const uint16_t r = f32_to_bf16_bits(bf16_bits_to_f32(residual[base + i]) + bf16_bits_to_f32(sublayer[base + i]));
+            residual[base + i] = r;
+            const float v = bf16_bits_to_f32(r);
+            ss = fmaf(v, v, ss);
+        }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += red[i];
+    const float inv = rsqrtf(total / (float)cols + eps);
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < kResNormPerThread; ++j) {
+            const int i = threadIdx.x + j * 256;
+            if (i < cols) normed[base + i] = f32_to_bf16_bits(keep[j] * inv * (bf16_bits_to_f32(w[i]) + (gemma ? 1.0f : 0.0f)));
+        }
+    } else {
+        for (int i = threadIdx.x; i < cols; i += 256) /* this thread re-reads only what it stored itself */
+            normed[base + i] = f32_to_bf16_bits(bf16_bits_to_f32(residual[base + i]) * inv * (bf16_bits_to_f32(w[i]) + (gemma ? 1.0f : 0.0f)));
+    }
+}
+
+int residual_norm(void *normed, void *residual, const void *sublayer, const void *w, int cols, int rows, float eps,
+                  int gemma, cudaStream_t stream) {
+    residual_norm_kernel<<<rows, 256, 0, stream>>>((uint16_t *)normed, (uint16_t *)residual, (const uint16_t *)sublayer,
+                                                   (const uint16_t *)w, cols, eps, gemma);
+    FFN_CUDA_TRY(cudaGetLastError(), "residual_norm launch");
+    return FFN_OK;
+}
+
+/* ------------------------------------------------------------------------------------------- */
+/* SiLU(gate) * up over a contiguous [gate[n] | up[n]] buffer (replaces kernel_silu_mul,         */
+/* csrc/kernels/silu.cu:29-52, which forwards to FlashInfer's act_and_mul): FP32, one rounding.  */
+/* ------------------------------------------------------------------------------------------- */
+__global__ void silu_mul_kernel(uint16_t *__restrict__ out, const uint16_t *__restrict__ gate, int n) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+        out[i] = f32_to_bf16_bits(silu_mul(bf16_bits_to_f32(gate[i]), bf16_bits_to_f32(gate[n + i])));
+}
+
+int silu_mul_pair(void *out, const void *gate, int n, cudaStream_t stream) {
+    silu_mul_kernel<<<(unsigned)min((n + 255) / 256, 1184), 256, 0, stream>>>((uint16_t *)out, (const uint16_t *)gate, n);
+    FFN_CUDA_TRY(cudaGetLastError(), "silu_mul launch");
+    return FFN_OK;
+}
+
 int gemma_rms_norm(void *out, const void *x, const void *w, int cols, int rows, float eps, int gemma,
                    cudaStream_t stream) {
     gemma_rms_norm_kernel<<<rows, 256, 0, stream>>>((uint16_t *)out, (const uint16_t *)x,

@@ -14,6 +14,9 @@ int silu_mul_packed(void *out, const void *packed, int tokens, int inter, cudaSt
 int gemma_rms_norm(void *out, const void *x, const void *w, int cols, int rows, float eps, int gemma,
                    cudaStream_t stream);
 int residual_add(void *dst, const void *src, int n, cudaStream_t stream);
+int residual_norm(void *normed, void *residual, const void *sublayer, const void *w, int cols, int rows, float eps,
+                  int gemma, cudaStream_t stream);
+int silu_mul_pair(void *out, const void *gate, int n, cudaStream_t stream);
 int dequantize_int4(void *out, const void *packed, const void *scales, int N, int K, int *bad,
                     cudaStream_t stream);
 

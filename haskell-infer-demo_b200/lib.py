@@ -82,6 +82,10 @@ def _declare(lib):
         "test_gemm_int4": [vp, vp, vp, vp, ci, ci, ci, ci],
         "test_silu_mul_packed": [vp, vp, ci, ci],
         "test_norm": [vp, vp, vp, ci, ci],
+        "test_silu_mul": [vp, vp, ci],
+        "test_residual_norm": [vp, vp, vp, vp, ci, ci, ctypes.c_float, ci],
+        "ffn_residual_norm": [vp, vp, vp, vp, ci, ci, ctypes.c_float, ci, vp],
+        "ffn_silu_mul": [vp, vp, ci, vp],
     }
     lib.ffn_quant_manifest_free.argtypes = [vp]
     lib.ffn_quant_manifest_free.restype = None

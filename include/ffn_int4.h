@@ -85,6 +85,19 @@ int ffn_silu_mul_packed(void *out, const void *packed, int tokens, int intermedi
 int ffn_gemma_rms_norm(void *out, const void *x, const void *weight, int cols, int rows, float eps,
                        void *stream);
 
+/* Replaces kernel_residual_norm (csrc/kernels/flashinfer_norm.cu:112-174; decl csrc/include/kernels.h): the
+ * residual update and the norm that follows it in one pass.  residual <- bf16(f32(residual) +
+ * f32(sublayer)) is stored, and normed = bf16(r * rsqrt(mean(r^2) + eps) * (weight + (gemma ? 1 : 0)))
+ * is computed from the ROUNDED r, as the reference's rounding rule requires.  All bf16 [rows][hidden]
+ * (weight [hidden]); same refusals ("invalid shape or epsilon", "null buffer") as status codes. */
+int ffn_residual_norm(void *normed, void *residual, const void *sublayer, const void *weight, int hidden, int rows,
+                      float eps, int gemma, void *stream);
+
+/* Replaces kernel_silu_mul (csrc/kernels/silu.cu:29-52): out[i] = bf16(silu(gate[i]) * gate[n + i]) over a
+ * contiguous [gate[n] | up[n]] bf16 buffer; same refusals (negative n; n >= 8 needs n % 8 == 0 and
+ * 16-byte aligned buffers). */
+int ffn_silu_mul(void *out, const void *gate, int n, void *stream);
+
 /* Replaces kernel_residual_add (csrc/kernels/gdn_norm.cu:121-136): dst = bf16(f32(dst)+f32(src)). */
 int ffn_residual_add(void *dst, const void *src, int n, void *stream);
 
@@ -292,6 +305,9 @@ int test_gemm_int4(void *out, const void *a, const void *packed, const void *sca
                    int K, int group);                                     /* kernel_bridge.cu:83-95 */
 int test_silu_mul_packed(void *out, const void *packed, int tokens, int intermediate); /* :68-79 */
 int test_norm(void *out, const void *x, const void *weight, int rows, int cols);       /* :31-41 */
+int test_silu_mul(void *out, const void *gate, int n);                                  /* :55-66 */
+int test_residual_norm(void *normed, void *residual, const void *sublayer, const void *weight, int hidden,
+                       int rows, float eps, int gemma);                                 /* :99-113 */
 
 #ifdef __cplusplus
 }

@@ -111,3 +111,62 @@ def test_silu_norm_residual(cuda):
     dst = dev_bits(o.bf16_bits(h), cuda).clone()
     ops.kernel_residual_add(dst, dev_bits(o.bf16_bits(y), cuda))
     assert np.array_equal(host_f32(dst), o.residual_add(h, y))
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 256), (4, 256), (3, 100), (2, 5000), (2, 5120), (1, 9000)])
+@pytest.mark.parametrize("gemma", [0, 1])
+def test_residual_norm_rounding_rule(cuda, rows, hidden, gemma):
+    """The reference's gate for the fused residual + norm (tests/test_residual_norm.py:30-150), through
+    the same bridge entry with host pointers: the updated residual is bitwise bf16(r + s); the norm is
+    within 8e-3 of the expression evaluated on the ROUNDED residual and no further from it than from
+    the one evaluated on the unrounded sum.  Shapes are the reference's plus the 27B row and one row
+    longer than the kernel keeps in registers."""
+    rng = np.random.default_rng(11 + rows * 7 + hidden + gemma)
+    res = o.bf16_round(rng.standard_normal((rows, hidden), dtype=np.float32) * np.float32(1.5))
+    sub = o.bf16_round(rng.standard_normal((rows, hidden), dtype=np.float32) * np.float32(1.5))
+    w = o.bf16_round(rng.standard_normal(hidden, dtype=np.float32) * np.float32(0.1))
+    kept = o.bf16_bits(res).copy()
+    normed = np.zeros((rows, hidden), np.uint16)
+    sub_bits, w_bits = o.bf16_bits(sub), o.bf16_bits(w)
+    st = L.load().test_residual_norm(normed.ctypes.data, kept.ctypes.data, sub_bits.ctypes.data, w_bits.ctypes.data,
+                                     hidden, rows, 1e-6, gemma)
+    assert st == 0
+    want_r = o.residual_add(res, sub)
+    assert np.array_equal(o.bf16_to_f32(kept), want_r)
+
+    def norm_of(total):
+        t64 = total.astype(np.float64)
+        inv = 1.0 / np.sqrt((t64 * t64).mean(axis=-1, keepdims=True) + 1e-6)
+        return o.bf16_round((t64 * inv * (w.astype(np.float64) + gemma)).astype(np.float32))
+    got = o.bf16_to_f32(normed)
+    want = norm_of(want_r)
+    plain = norm_of(res.astype(np.float32) + sub.astype(np.float32))
+    assert np.abs(got - want).max() / max(np.abs(want).max(), 1e-6) <= 8e-3
+    assert np.abs(got - want).mean() <= np.abs(got - plain).mean()
+
+
+def test_residual_norm_and_silu_mul_refusals(cuda):
+    lib = L.load()
+    buf = torch.zeros(64, dtype=torch.bfloat16, device=cuda)
+    p = buf.data_ptr()
+    assert lib.ffn_residual_norm(p, p, p, p, 0, 1, 1e-6, 1, None) == -4       # invalid shape
+    assert lib.ffn_residual_norm(p, p, p, p, 16, 1, 0.0, 1, None) == -4       # invalid epsilon
+    assert lib.ffn_residual_norm(p, None, p, p, 16, 1, 1e-6, 1, None) == -4   # null buffer
+    assert lib.ffn_residual_norm(p, p, p, p, 16, 0, 1e-6, 1, None) == 0                     # no rows: nothing to do
+    assert lib.ffn_silu_mul(p, p, -1, None) == -4
+    assert lib.ffn_silu_mul(p, p + 2, 16, None) == -4                         # misaligned
+    assert lib.ffn_silu_mul(p, p, 12, None) == -4                             # n >= 8 must be a multiple of 8
+    assert lib.ffn_silu_mul(p, p, 0, None) == 0
+
+
+@pytest.mark.parametrize("n", [4, 8, 1024, 17408])
+def test_silu_mul_pair(cuda, n):
+    """kernel_silu_mul's contract (csrc/kernels/silu.cu:29-52): contiguous [gate[n] | up[n]], FP32 SiLU*up,
+    one rounding; checked as tests/test_library_ops.py does (within one BF16 step of the FP64 value)."""
+    rng = np.random.default_rng(n)
+    gu = o.bf16_round(rng.standard_normal(2 * n, dtype=np.float32) * 3)
+    bits = o.bf16_bits(gu)
+    out = np.zeros(n, np.uint16)
+    assert L.load().test_silu_mul(out.ctypes.data, bits.ctypes.data, n) == 0
+    want = o.silu_mul(gu[:n], gu[n:])
+    assert np.abs(o.bf16_to_f32(out) - want).max() <= 2.0 ** -7 * max(1.0, np.abs(want).max())
