@@ -94,17 +94,9 @@ class ClockSampler:
 # synthetic layer, generated on the device (N(0, 0.02) weights quantized with the format's rule)
 # ------------------------------------------------------------------------------------------------
 def quantize_on_device(w):
-    """torch restatement of the format (group 128, s = bf16(max|w|/7), RNE codes clipped to +-7,
-    low K index in the low nibble).  Bench data only; the parity tests use the CPU oracle."""
-    import torch
-    n, k = w.shape
-    g = w.view(n, k // 128, 128)
-    amax = g.abs().amax(dim=2)
-    scale = torch.where(amax == 0, torch.ones_like(amax), amax / 7.0).to(torch.bfloat16)
-    q = torch.clamp(torch.round(g / scale.float().unsqueeze(2)), -7, 7).to(torch.int32).view(n, k)
-    nib = (q & 0xF).to(torch.uint8)
-    packed = nib[:, 0::2] | (nib[:, 1::2] << 4)
-    return packed.contiguous(), scale.contiguous()
+    """The library's GPU quantizer (byte-identical to the reference's format)."""
+    from haskell_infer_demo_b200.ops import quantize_int4
+    return quantize_int4(w.contiguous())
 
 
 def make_rank_layer(dev, h, i, tp, rank, seed):

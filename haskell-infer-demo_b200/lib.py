@@ -86,6 +86,7 @@ def _declare(lib):
         "test_residual_norm": [vp, vp, vp, vp, ci, ci, ctypes.c_float, ci],
         "ffn_residual_norm": [vp, vp, vp, vp, ci, ci, ctypes.c_float, ci, vp],
         "ffn_silu_mul": [vp, vp, ci, vp],
+        "ffn_quantize_int4": [vp, vp, vp, ctypes.c_longlong, ctypes.c_longlong, vp],
     }
     lib.ffn_quant_manifest_free.argtypes = [vp]
     lib.ffn_quant_manifest_free.restype = None

@@ -64,6 +64,19 @@ def kernel_residual_add(dst, src):
     return dst
 
 
+def quantize_int4(weights):
+    """FP32 [N, K] on the device -> (packed u8 [N, K/2], scales bf16 [N, K/128]), the bytes the
+    reference's quantizer writes (include/ffn_int4.h, ffn_quantize_int4)."""
+    _require_cuda(weights)
+    if weights.dtype != torch.float32 or weights.dim() != 2 or not weights.is_contiguous():
+        raise ValueError("quantize_int4 takes a contiguous FP32 [N, K] tensor")
+    n, k = weights.shape
+    packed = torch.empty((n, k // 2), dtype=torch.uint8, device=weights.device)
+    scales = torch.empty((n, k // 128), dtype=torch.bfloat16, device=weights.device)
+    check(load().ffn_quantize_int4(_ptr(weights), _ptr(packed), _ptr(scales), n, k, _stream()))
+    return packed, scales
+
+
 def dequantize_int4(packed, scales):
     """float(code) * float(scale) through the kernels' unpack routine -> (fp32 [N, K], count of
     reserved 0x8 nibbles)."""

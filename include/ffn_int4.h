@@ -101,6 +101,17 @@ int ffn_silu_mul(void *out, const void *gate, int n, void *stream);
 /* Replaces kernel_residual_add (csrc/kernels/gdn_norm.cu:121-136): dst = bf16(f32(dst)+f32(src)). */
 int ffn_residual_add(void *dst, const void *src, int n, void *stream);
 
+/* Replaces linear_quantize_int4 (csrc/include/linear_weight.h; csrc/linear_weight.cpp:108-176), which the
+ * reference's offline converter reaches once per tensor through a subprocess
+ * (scripts/quantize_weights.py:136-156), for weights that are in device memory: FP32 [n][k] ->
+ * packed [n][k/2] and BF16 scales [n][k/128], byte-identical to the reference's output (group
+ * maximum, scale = BF16_RNE(max/7) with 1.0 for an all-zero group, q = clip(nearbyint(w/scale),
+ * -7, 7) against the rounded scale, low K index in the low nibble).  Same refusals, reported before
+ * anything is written: k % 128, n % 8 (FFN_ERR_CONFIG); a non-finite element, or a group whose scale
+ * does not round to a positive finite BF16 (FFN_ERR_WEIGHTS, the message names the element or the
+ * row and group).  Synchronises `stream` (the refusals need the checking pass's answer). */
+int ffn_quantize_int4(const void *weights, void *packed, void *scales, long long n, long long k, void *stream);
+
 /* Writes float(code) * float(scale) for every element of a packed [N][K] weight to out (FP32
  * [N][K]) using the same unpack routine the GEMV kernels use.  Exists so the "dequantized
  * weights are bit-exact" bar can be checked against linear_dequantize_int4
