@@ -285,9 +285,10 @@ def run_ours(args):
         if world == 1 and not args.no_cpu and not args.layers:
             line["cpu_baseline"] = cpu_baseline(h, i, m, budget_s=12.0)
         print(json.dumps(line), flush=True)
-    if comm is not None:
+    if world > 1:
         barrier()
-        comm.close()
+        if comm is not None:
+            comm.close()
         dist.destroy_process_group()
 
 
