@@ -285,11 +285,12 @@ def run_ours(args):
         if world == 1 and not args.no_cpu and not args.layers:
             line["cpu_baseline"] = cpu_baseline(h, i, m, budget_s=12.0)
         print(json.dumps(line), flush=True)
-    if world > 1:
+    if comm is not None:
         barrier()
-        if comm is not None:
-            comm.close()
+        comm.close()
         dist.destroy_process_group()
+    # The comparison variant leaves its process group to interpreter exit: tearing NCCL down while the
+    # captured graph that holds its collectives is alive did not return on 8 GPUs.
 
 
 # ------------------------------------------------------------------------------------------------
