@@ -133,6 +133,25 @@ extern "C" {
 const char *ffn_int4_last_error(void) { return g_error; }
 int ffn_int4_abi_version(void) { return FFN_INT4_ABI_VERSION; }
 
+int ffn_int4_describe_plan(int tokens, int hidden, int intermediate, int sm_count, int smem_optin, char *out,
+                           size_t out_bytes) {
+    clear_error();
+    if (!out || out_bytes < 64) return fail(FFN_ERR_CONFIG, "ffn_int4_describe_plan: the text buffer is too small");
+    if (tokens < 1 || hidden <= 0 || intermediate <= 0 || hidden % FFN_INT4_GROUP || intermediate % FFN_INT4_GROUP ||
+        sm_count < 1 || smem_optin < 1)
+        return fail(FFN_ERR_CONFIG, "ffn_int4_describe_plan: invalid shape or device description");
+    if (tokens <= 2 && fused_describe_plan(tokens, hidden, intermediate, sm_count, smem_optin, out, out_bytes)) return FFN_OK;
+    if (mma_describe_plan(tokens < 64 ? tokens : 64, hidden, intermediate, sm_count, smem_optin, out, out_bytes)) {
+        if (tokens > 64) { /* longer batches go through the pair in blocks of 64 tokens */
+            const size_t used = strlen(out);
+            snprintf(out + used, out_bytes - used, " passes=%d", (tokens + 63) / 64);
+        }
+        return FFN_OK;
+    }
+    snprintf(out, out_bytes, "kernel=generic launches=3 (gate/up GEMM, SiLU*up, down GEMM)");
+    return FFN_OK;
+}
+
 int ffn_int4_set_fused(int enabled) {
     const int old = g_fused_enabled;
     g_fused_enabled = enabled != 0;

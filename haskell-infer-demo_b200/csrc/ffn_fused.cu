@@ -26,14 +26,16 @@
  *                 the cross-GPU exchange.
  *
  * Cross-rank reduce (TP = R > 1): CTA c of every rank owns the same output rows.  Its epilogue
- * stores the FP32 partials of those rows into slot `rank` of a [2][R][M][H] buffer in EVERY rank's
- * memory (plain peer stores over NVLink), publishes them with a system-scope release increment of
- * flag[c] on every rank, waits (bounded) until its own flag[c] shows all R arrivals, then adds the R
- * slots in rank order and rounds once to BF16.  No collective call and no second kernel.
+ * sends the FP32 partial sums of those rows into slot `rank` of a [2][R][M][H] buffer in EVERY rank's
+ * memory (peer stores over NVLink), each as one 8-byte word {value, call number + 1}, tile by tile
+ * while phase 2 runs; at the end it polls (bounded) the words of its own rows in its own memory
+ * until all R carry this call's number, adds them in rank order and rounds once to BF16.  No fence,
+ * no flag, no collective call and no second kernel.
  *
  * Every device-side wait is bounded; on expiry the kernel records where it gave up in the status
  * word, drains its own copies and returns.  The host maps that to FFN_ERR_CUDA.
  */
+#include <stdio.h>
 #include <stdlib.h>
 
 #include <mutex>
@@ -55,7 +57,7 @@ constexpr uint32_t kSpinLimit = 1u << 22;              /* bounded waits: polls o
 
 /* status word values (where a wait gave up) */
 enum { ST_OK = 0, ST_PRODUCER_EMPTY = 1, ST_CONSUMER_FULL = 2, ST_PART_EMPTY = 3, ST_PART_FULL = 4,
-       ST_GRID_BARRIER = 5, ST_PEER_FLAG = 6, ST_DRAIN = 7, ST_X_FULL = 8 };
+       ST_GRID_BARRIER = 5, ST_PEER_DATA = 6, ST_DRAIN = 7, ST_X_FULL = 8 };
 
 struct PhasePlan {
     const uint8_t *w;     /* packed rows */
@@ -82,7 +84,7 @@ struct FusedParams {
     int tp, rank;
     unsigned long long *const *peer_slots; /* device array [tp]: each rank's [2][tp][M_max][H] tagged words */
     int slot_stride;      /* elements per (parity, rank) slot = M_max * H */
-    unsigned *tp_seq;     /* this communicator's call counter (slot parity, flag target) */
+    unsigned *tp_seq;     /* this communicator's call counter (slot parity, tag of the exchanged words) */
     /* optional fused residual update with the reduced output y: h <- bf16(h + y); NULL = off */
     uint16_t *residual;
     /* optional fused RMSNorm of the input (x is then the residual stream h): n = bf16(h * rsqrt(mean(h^2)
@@ -696,7 +698,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
                         all_in = in;
                         a += v;
                     }
-                    if (!all_in) { give_up(sm, P.sync, ST_PEER_FLAG); break; }
+                    if (!all_in) { give_up(sm, P.sync, ST_PEER_DATA); break; }
                     const float y = round_bf16(a);
                     P.out[(size_t)m * P.H + row] = f32_to_bf16_bits(y);
                     if (P.residual)
@@ -708,7 +710,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
         }
     }
     __syncthreads();
-    /* the call sequence number advances once per launch (parity of the peer slots, flag target) */
+    /* the call sequence number advances once per launch (parity of the peer slots, tag of the exchanged words) */
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         P.sync[1] += gridDim.x; /* every CTA has arrived by now (this CTA passed the barrier) */
         if (P.tp > 1) atomicAdd(P.tp_seq, 1u);
@@ -787,6 +789,34 @@ static bool plan_phase(PhasePlan &pl, int K, int MT, bool pairs, int target_byte
     return true;
 }
 
+/* The whole geometry of a launch from the shape alone (no device needed): the two phases' thread
+ * layouts and tiles, the stage size, how many stages the shared memory holds.  Pointers are left to
+ * the caller.  Returns false when the kernel does not take the shape. */
+static bool plan_fused(FusedParams &P, int tokens, int H, int I, int smem_optin, int target_bytes, int &c1, int &c2,
+                       size_t &smem) {
+    if (tokens < 1 || tokens > 2) return false;
+    if (H <= 0 || I <= 0 || H % FFN_INT4_GROUP || I % FFN_INT4_GROUP) return false;
+    if (H > (1 << 22) || I > (1 << 22)) return false; /* 32-bit row partitioning in the kernel */
+    P.M = tokens; P.H = H; P.I = I;
+    if (!plan_phase(P.p1, H, tokens, true, target_bytes, c1)) return false;
+    if (!plan_phase(P.p2, I, tokens, false, target_bytes, c2)) return false;
+    P.p1.rows_total = I; P.p1.up_offset = I;
+    P.p2.rows_total = H; P.p2.up_offset = 0;
+    const int part_floats = tokens == 1 ? kPartFloats1 : kPartFloats2;
+    if (P.p1.TR * 2 * tokens * P.p1.nhw > part_floats || P.p2.TR * tokens * P.p2.nhw > part_floats) return false;
+    P.stage_w_bytes = round_up(max(2 * P.p1.TR * P.p1.rb, P.p2.TR * P.p2.rb), 128);
+    P.sc_half_bytes = round_up(max(P.p1.TR * P.p1.G * 2, P.p2.TR * P.p2.G * 2) + 32, 16);
+    P.stage_bytes = round_up(P.stage_w_bytes + 2 * P.sc_half_bytes, 128);
+    P.xs_bytes = round_up(tokens * I * 2, 128); /* act only: x is read from global memory */
+    const size_t fixed = fused_smem_header(tokens) + (size_t)P.xs_bytes;
+    if (fixed + 2 * (size_t)P.stage_bytes > (size_t)smem_optin) return false;
+    P.nstages = (int)min((size_t)kMaxStages, ((size_t)smem_optin - fixed) / (size_t)P.stage_bytes);
+    if (P.nstages < 2) return false;
+    smem = fixed + (size_t)P.nstages * P.stage_bytes;
+    return true;
+}
+constexpr int kDefaultStageTarget = 62 * 1024; /* bytes of weights per stage the planner aims for */
+
 template <int C1, int C2, int MT>
 static int launch_fused(DeviceState &d, const FusedParams &P, int grid, size_t smem, cudaStream_t stream) {
     bool &set = d.attr_set[C1 - 1][C2 - 1][MT - 1];
@@ -805,14 +835,13 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
                      const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual,
                      const FusedNorm *norm) {
     if (tokens < 1 || tokens > 2) return FFN_NOT_ADMITTED;
-    if (H > (1 << 22) || I > (1 << 22)) return FFN_NOT_ADMITTED; /* 32-bit row partitioning in the kernel */
     DeviceState *dp = nullptr;
     const int st = device_state(&dp);
     if (st) return st;
     DeviceState &d = *dp;
     if (!d.cooperative) return FFN_NOT_ADMITTED;
     if (((uintptr_t)w->gate_up_i4 & 15) || ((uintptr_t)w->down_i4 & 15) || ((uintptr_t)normed & 15) ||
-        ((uintptr_t)act & 15))
+        ((uintptr_t)act & 15) || ((uintptr_t)w->gate_up_i4_scales & 15) || ((uintptr_t)w->down_i4_scales & 15))
         return FFN_NOT_ADMITTED;
 
     FusedParams P = {};
@@ -833,30 +862,15 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
         P.tp_seq = tp->seq;
         if (tokens * H > tp->slot_stride) return fail(FFN_ERR_CONFIG, "fused FFN: %d tokens exceed the exchange buffer", tokens);
     }
-    static const int target_kb = getenv("FFN_INT4_STAGE_KB") ? atoi(getenv("FFN_INT4_STAGE_KB")) : 62; /* tuning knob */
-    const int target = target_kb * 1024;
+    static const int target_kb = getenv("FFN_INT4_STAGE_KB") ? atoi(getenv("FFN_INT4_STAGE_KB")) : kDefaultStageTarget / 1024; /* tuning knob */
     int c1 = 0, c2 = 0;
-    if (!plan_phase(P.p1, H, tokens, true, target, c1)) return FFN_NOT_ADMITTED;
-    if (!plan_phase(P.p2, I, tokens, false, target, c2)) return FFN_NOT_ADMITTED;
+    size_t smem = 0;
+    if (!plan_fused(P, tokens, H, I, d.smem_optin, target_kb * 1024, c1, c2, smem)) return FFN_NOT_ADMITTED;
     P.p1.w = w->gate_up_i4; P.p1.s = (const uint16_t *)w->gate_up_i4_scales;
-    P.p1.rows_total = I; P.p1.up_offset = I;
     P.p2.w = w->down_i4; P.p2.s = (const uint16_t *)w->down_i4_scales;
-    P.p2.rows_total = H; P.p2.up_offset = 0;
-    if (P.p1.TR * 2 * tokens * P.p1.nhw > (tokens == 1 ? kPartFloats1 : kPartFloats2) || P.p2.TR * tokens * P.p2.nhw > (tokens == 1 ? kPartFloats1 : kPartFloats2))
-        return FFN_NOT_ADMITTED;
-    if (((uintptr_t)w->gate_up_i4_scales & 15) || ((uintptr_t)w->down_i4_scales & 15)) return FFN_NOT_ADMITTED;
-    P.stage_w_bytes = round_up(max(2 * P.p1.TR * P.p1.rb, P.p2.TR * P.p2.rb), 128);
-    P.sc_half_bytes = round_up(max(P.p1.TR * P.p1.G * 2, P.p2.TR * P.p2.G * 2) + 32, 16);
-    P.stage_bytes = round_up(P.stage_w_bytes + 2 * P.sc_half_bytes, 128);
-    P.xs_bytes = round_up(tokens * I * 2, 128); /* act only: x is read from global memory */
     P.trace = g_trace;
     static const int debug_flags = getenv("FFN_INT4_DEBUG") ? atoi(getenv("FFN_INT4_DEBUG")) : 0;
     P.debug = debug_flags;
-    const size_t fixed = fused_smem_header(tokens) + (size_t)P.xs_bytes;
-    if (fixed + 2 * (size_t)P.stage_bytes > (size_t)d.smem_optin) return FFN_NOT_ADMITTED;
-    P.nstages = (int)min((size_t)kMaxStages, ((size_t)d.smem_optin - fixed) / (size_t)P.stage_bytes);
-    if (P.nstages < 2) return FFN_NOT_ADMITTED;
-    const size_t smem = fixed + (size_t)P.nstages * P.stage_bytes;
     const int grid = d.sm_count; /* under TP every rank runs the same grid: CTA c owns the same rows everywhere */
 
 #define FFN_LAUNCH(A, B, C) return launch_fused<A, B, C>(d, P, grid, smem, stream)
@@ -944,24 +958,13 @@ int fused_ffn_launch_noalloc(cudaStream_t stream, const void *normed, void *laye
     P.M = tokens; P.H = H; P.I = I;
     P.sync = d.sync;
     P.tp = 1; P.rank = 0;
-    const int target = 62 * 1024;
     int c1 = 0, c2 = 0;
-    if (!plan_phase(P.p1, H, tokens, true, target, c1) || !plan_phase(P.p2, I, tokens, false, target, c2))
-        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: rows of %d / %d columns do not fit the kernel", H, I);
+    size_t smem = 0;
+    if (!plan_fused(P, tokens, H, I, d.smem_optin, kDefaultStageTarget, c1, c2, smem))
+        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: rows of %d / %d columns do not fit the kernel's "
+                    "shared memory", H, I);
     P.p1.w = w->gate_up_i4; P.p1.s = (const uint16_t *)w->gate_up_i4_scales;
-    P.p1.rows_total = I; P.p1.up_offset = I;
     P.p2.w = w->down_i4; P.p2.s = (const uint16_t *)w->down_i4_scales;
-    P.p2.rows_total = H; P.p2.up_offset = 0;
-    P.stage_w_bytes = round_up(max(2 * P.p1.TR * P.p1.rb, P.p2.TR * P.p2.rb), 128);
-    P.sc_half_bytes = round_up(max(P.p1.TR * P.p1.G * 2, P.p2.TR * P.p2.G * 2) + 32, 16);
-    P.stage_bytes = round_up(P.stage_w_bytes + 2 * P.sc_half_bytes, 128);
-    P.xs_bytes = round_up(tokens * I * 2, 128); /* act only: x is read from global memory */
-    const size_t fixed = fused_smem_header(tokens) + (size_t)P.xs_bytes;
-    if (P.p1.TR * 2 * tokens * P.p1.nhw > (tokens == 1 ? kPartFloats1 : kPartFloats2) || P.p2.TR * tokens * P.p2.nhw > (tokens == 1 ? kPartFloats1 : kPartFloats2) ||
-        fixed + 2 * (size_t)P.stage_bytes > (size_t)d.smem_optin)
-        return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_prepared_noalloc: the shape does not fit shared memory");
-    P.nstages = (int)min((size_t)kMaxStages, ((size_t)d.smem_optin - fixed) / (size_t)P.stage_bytes);
-    const size_t smem = fixed + (size_t)P.nstages * P.stage_bytes;
     /* The array keeps whatever the previous call left.  The barrier words must be consistent with
      * each other and the status word must start at zero, so they are cleared on the stream first;
      * act needs no clearing (phase 1 writes every element phase 2 reads). */
@@ -974,6 +977,22 @@ int fused_ffn_launch_noalloc(cudaStream_t stream, const void *normed, void *laye
         return launch_fused<2, 2, 1>(d, P, grid, smem, stream);
     }
     return launch_fused<1, 1, 2>(d, P, grid, smem, stream);
+}
+
+/* Text description of what a launch of this shape would look like on a device with `sm_count` SMs
+ * and `smem_optin` bytes of opt-in shared memory; needs no device.  Returns false when the kernel
+ * does not take the shape. */
+bool fused_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin, char *out, size_t out_bytes) {
+    FusedParams P = {};
+    int c1 = 0, c2 = 0;
+    size_t smem = 0;
+    if (!plan_fused(P, tokens, H, I, smem_optin, kDefaultStageTarget, c1, c2, smem)) return false;
+    snprintf(out, out_bytes,
+             "kernel=fused grid=%d threads=%d smem=%zu stages=%d stage_bytes=%d act_bytes=%d "
+             "p1_cit=%d p1_ct=%d p1_rg=%d p1_jt=%d p1_pairs_per_tile=%d p2_cit=%d p2_ct=%d p2_rg=%d p2_jt=%d p2_rows_per_tile=%d",
+             sm_count, kThreads, smem, P.nstages, P.stage_bytes, P.xs_bytes, c1, P.p1.CT, P.p1.RG, P.p1.JT, P.p1.TR, c2,
+             P.p2.CT, P.p2.RG, P.p2.JT, P.p2.TR);
+    return true;
 }
 
 int fused_status_word(unsigned **out) {

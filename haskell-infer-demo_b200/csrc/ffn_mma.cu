@@ -27,6 +27,8 @@
  * per block; each writes FP32 partial sums to global memory and the last one to arrive adds them in
  * split order (deterministic) and runs the epilogue.
  */
+#include <stdio.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -347,17 +349,21 @@ struct MmaScratch {
 };
 static MmaScratch g_mma_scratch[64];
 
-template <int NT>
-static int launch_pair(MmaParams &A, MmaParams &B, int smem_optin, int sm_count, cudaStream_t stream) {
+/* Launch geometry of the pair for `nt` 8-token tiles: pipeline depth, shared memory per CTA, CTAs per
+ * SM, and the K splits of the down projection (chosen to fill the device's CTA slots as evenly as
+ * possible).  Needs no device.  Returns false when the tokens do not fit shared memory. */
+struct MmaPlan {
+    int stages, smem, per_sm, splits, gate_up_ctas, down_ctas;
+};
+static bool mma_plan(int nt, int H, int I, int smem_optin, int sm_count, MmaPlan &pl) {
     /* four stages when two CTAs still fit on an SM, else three if that makes two fit, else four */
     int stages = 4;
-    if (2 * (mma_smem(NT, 4) + 1024) > smem_optin && 2 * (mma_smem(NT, 3) + 1024) <= smem_optin) stages = 3;
-    while (stages > 2 && mma_smem(NT, stages) > smem_optin) --stages;
-    const int smem = mma_smem(NT, stages);
-    if (smem > smem_optin) return fail(FFN_ERR_CONFIG, "batched INT4 FFN: %d tokens do not fit shared memory", NT * 8);
+    if (2 * (mma_smem(nt, 4) + 1024) > smem_optin && 2 * (mma_smem(nt, 3) + 1024) <= smem_optin) stages = 3;
+    while (stages > 2 && mma_smem(nt, stages) > smem_optin) --stages;
+    const int smem = mma_smem(nt, stages);
+    if (smem > smem_optin) return false;
     const int per_sm = 2 * (smem + 1024) <= smem_optin ? 2 : 1;
-    /* K splits of the down projection: fill the CTA slots of the device as evenly as possible */
-    const int blocks = B.N / kMmaRows, slots = sm_count * per_sm, G = B.K / FFN_INT4_GROUP;
+    const int blocks = H / kMmaRows, slots = sm_count * per_sm, G = I / FFN_INT4_GROUP;
     int best = 1;
     double best_eff = 0.0;
     for (int sp = 1; sp <= kMmaMaxSplits && sp * 2 <= max(G, 2); ++sp) {
@@ -365,7 +371,18 @@ static int launch_pair(MmaParams &A, MmaParams &B, int smem_optin, int sm_count,
         const double eff = (double)units / (double)(((units + slots - 1) / slots) * slots);
         if (eff > best_eff + 1e-9) { best_eff = eff; best = sp; }
     }
-    B.splits = best;
+    pl.stages = stages; pl.smem = smem; pl.per_sm = per_sm; pl.splits = best;
+    pl.gate_up_ctas = I / (kMmaRows / 2); pl.down_ctas = blocks * best;
+    return true;
+}
+
+template <int NT>
+static int launch_pair(MmaParams &A, MmaParams &B, int smem_optin, int sm_count, cudaStream_t stream) {
+    MmaPlan pl;
+    if (!mma_plan(NT, B.N, B.K, smem_optin, sm_count, pl))
+        return fail(FFN_ERR_CONFIG, "batched INT4 FFN: %d tokens do not fit shared memory", NT * 8);
+    const int stages = pl.stages, smem = pl.smem, blocks = B.N / kMmaRows;
+    B.splits = pl.splits;
     FFN_CUDA_TRY(cudaFuncSetAttribute(gate_up_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "gate/up MMA: shared-memory opt-in");
     FFN_CUDA_TRY(cudaFuncSetAttribute(down_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "down MMA: shared-memory opt-in");
     gate_up_mma_kernel<NT><<<A.up_offset / (kMmaRows / 2), kMmaThreads, smem, stream>>>(A, stages);
@@ -373,6 +390,19 @@ static int launch_pair(MmaParams &A, MmaParams &B, int smem_optin, int sm_count,
     down_mma_kernel<NT><<<blocks * B.splits, kMmaThreads, smem, stream>>>(B, stages);
     FFN_CUDA_TRY(cudaGetLastError(), "down MMA launch");
     return FFN_OK;
+}
+
+static int mma_tiles_for(int tokens) { return tokens <= 8 ? 1 : tokens <= 16 ? 2 : tokens <= 32 ? 4 : 8; }
+
+bool mma_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin, char *out, size_t out_bytes) {
+    if (tokens < 1 || tokens > 64 || H <= 0 || I <= 0 || H % kMmaRows || I % (kMmaRows / 2) || I % FFN_INT4_GROUP) return false;
+    MmaPlan pl;
+    const int nt = mma_tiles_for(tokens);
+    if (!mma_plan(nt, H, I, smem_optin, sm_count, pl)) return false;
+    snprintf(out, out_bytes,
+             "kernel=mma_pair token_tiles=%d threads=%d smem=%d stages=%d ctas_per_sm=%d gate_up_ctas=%d down_ctas=%d down_k_splits=%d",
+             nt, kMmaThreads, pl.smem, pl.stages, pl.per_sm, pl.gate_up_ctas, pl.down_ctas, pl.splits);
+    return true;
 }
 
 /* normed bf16 [tokens][H] -> layer_out bf16 [tokens][H]; `act` receives act in natural order. */
@@ -424,10 +454,12 @@ int mma_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *lay
         B.tp = tp->tp; B.rank = tp->rank; B.slot_stride = tp->slot_stride;
         B.peer_slots = tp->peer_slots; B.tp_seq = tp->seq;
     }
-    if (tokens <= 8) return launch_pair<1>(A, B, smem_optin, sm_count, stream);
-    if (tokens <= 16) return launch_pair<2>(A, B, smem_optin, sm_count, stream);
-    if (tokens <= 32) return launch_pair<4>(A, B, smem_optin, sm_count, stream);
-    return launch_pair<8>(A, B, smem_optin, sm_count, stream);
+    switch (mma_tiles_for(tokens)) {
+        case 1: return launch_pair<1>(A, B, smem_optin, sm_count, stream);
+        case 2: return launch_pair<2>(A, B, smem_optin, sm_count, stream);
+        case 4: return launch_pair<4>(A, B, smem_optin, sm_count, stream);
+        default: return launch_pair<8>(A, B, smem_optin, sm_count, stream);
+    }
 }
 
 }  // namespace ffn

@@ -17,6 +17,9 @@ int residual_add(void *dst, const void *src, int n, cudaStream_t stream);
 int residual_norm(void *normed, void *residual, const void *sublayer, const void *w, int cols, int rows, float eps,
                   int gemma, cudaStream_t stream);
 int silu_mul_pair(void *out, const void *gate, int n, cudaStream_t stream);
+/* Launch geometry as text, computed from the shape alone (no device needed); false = the kernel does not take the shape. */
+bool fused_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin, char *out, size_t out_bytes);
+bool mma_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin, char *out, size_t out_bytes);
 int dequantize_int4(void *out, const void *packed, const void *scales, int N, int K, int *bad,
                     cudaStream_t stream);
 

@@ -87,6 +87,7 @@ def _declare(lib):
         "ffn_residual_norm": [vp, vp, vp, vp, ci, ci, ctypes.c_float, ci, vp],
         "ffn_silu_mul": [vp, vp, ci, vp],
         "ffn_quantize_int4": [vp, vp, vp, ctypes.c_longlong, ctypes.c_longlong, vp],
+        "ffn_int4_describe_plan": [ci, ci, ci, ci, ci, ctypes.c_char_p, ctypes.c_size_t],
     }
     lib.ffn_quant_manifest_free.argtypes = [vp]
     lib.ffn_quant_manifest_free.restype = None

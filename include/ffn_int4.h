@@ -51,6 +51,14 @@ int ffn_int4_abi_version(void);
  * (csrc/engine.cu:1723-1730).  No counterpart function in the reference. */
 int ffn_int4_device_status(int *where, int *cta);
 
+/* Which kernel a call of this shape takes and its launch geometry (grid, shared memory, pipeline
+ * stages, tile sizes, K splits), as one line of key=value text, for a device with `sm_count` SMs and
+ * `smem_optin` bytes of opt-in shared memory per block.  Pure host arithmetic: needs no GPU, so the
+ * planning can be checked for any shape anywhere.  `intermediate` is the rank-local size.  No
+ * counterpart in the reference (its launch shapes are fixed constants, csrc/kernels/gemm_quant.cu:20-31). */
+int ffn_int4_describe_plan(int tokens, int hidden, int intermediate, int sm_count, int smem_optin, char *out,
+                           size_t out_bytes);
+
 /* Debugging aid: when given a device buffer of 16 int64, CTA 0 of every later fused launch writes
  * clock64() stamps of its pipeline events there (NULL switches it off).  No counterpart in the
  * reference (its profiler times whole regions with events, csrc/profile.cu:114-144). */

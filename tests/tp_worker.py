@@ -6,7 +6,7 @@
 Every rank draws the same seeded configuration, keeps its slice (gate/up rows, down columns, global
 scales), runs the FFN with the in-kernel cross-rank reduce and checks: (1) the result against the
 TP=1 CPU oracle at the stated bars, (2) bit-identical results on every rank, (3) repeatability over
-many back-to-back calls (flags and slots are reused), (4) the fused residual update.
+many back-to-back calls (the exchange slots are reused), (4) the fused residual update.
 """
 import os
 import sys
@@ -57,7 +57,7 @@ def main():
         dist.all_gather(gathered, got_t)
         for r in range(world):
             assert torch.equal(gathered[r].view(torch.int16), got_t.view(torch.int16)), f"rank {r} differs"
-        # repeatable: slots and flags are reused call after call
+        # repeatable: the exchange slots are reused call after call
         for _ in range(25):
             again = comm.forward_mlp(mlp, xd)
         L.device_status()
