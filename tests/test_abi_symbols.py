@@ -49,3 +49,46 @@ def test_struct_mirrors_match_header_sizes():
     import ctypes
     assert ctypes.sizeof(L.MlpWeights) == 8 * 8 + 8      # eight pointers + int, padded
     assert ctypes.sizeof(L.ModelDims) == 25 * 4
+
+
+def test_new_entries_validate_before_any_cuda_call():
+    lib = L.load()
+    assert lib.ffn_residual_norm(16, 16, 16, 16, 0, 1, 1e-6, 1, None) == -4
+    assert b"invalid shape or epsilon" in lib.ffn_int4_last_error()
+    assert lib.ffn_residual_norm(16, None, 16, 16, 128, 1, 1e-6, 1, None) == -4
+    assert b"null buffer" in lib.ffn_int4_last_error()
+    assert lib.ffn_residual_norm(None, None, None, None, 128, 0, 1e-6, 0, None) == 0     # no rows: nothing to do
+    assert lib.ffn_silu_mul(16, 16, -1, None) == -4
+    assert lib.ffn_silu_mul(16, 18, 16, None) == -4                                     # misaligned gate
+    assert lib.ffn_quantize_int4(16, 16, 16, 8, 192, None) == -4
+    assert b"whole number" in lib.ffn_int4_last_error()
+    assert lib.ffn_quantize_int4(16, 16, 16, 12, 128, None) == -4
+    assert b"8-row tile" in lib.ffn_int4_last_error()
+    assert lib.ffn_quantize_int4(None, 16, 16, 8, 128, None) == -4
+
+
+def test_compute_entries_fail_loudly_without_a_gpu():
+    """There is no CPU fallback: on a machine without a CUDA device every compute entry point returns
+    an error status with a message, it never computes on the host."""
+    import ctypes
+
+    import numpy as np
+    import torch
+    if torch.cuda.is_available():
+        import pytest
+        pytest.skip("this machine has a GPU")
+    lib = L.load()
+    buf = np.zeros(4096, np.uint16)
+    p = buf.ctypes.data
+    assert lib.ffn_gemm_int4_bf16(p, p, p, p, 1, 8, 128, 128, None) < 0 and lib.ffn_int4_last_error()
+    assert lib.ffn_quantize_int4(p, p, p, 8, 128, None) < 0 and lib.ffn_int4_last_error()
+    assert lib.test_gemm_int4(p, p, p, p, 1, 8, 128, 128) != 0
+    handle = ctypes.c_void_p()
+    assert lib.ffn_tp_create(ctypes.byref(handle), 2, 0, 1024, 2) < 0
+    assert b"CUDA" in lib.ffn_int4_last_error()
+    w, d = L.MlpWeights(), L.ModelDims()
+    w.gate_up_i4 = w.gate_up_i4_scales = w.down_i4 = w.down_i4_scales = p
+    w.i4_group = 128
+    d.hidden_size, d.intermediate_size, d.max_chunk, d.rms_eps = 128, 128, 128, 1e-6
+    assert lib.ffn_forward_mlp_prepared(None, None, p, p, p, ctypes.byref(w), 1, ctypes.byref(d)) < 0
+    assert lib.ffn_int4_last_error()
