@@ -315,6 +315,30 @@ int ffn_load_quantized_ffn_ranks(const char *manifest_dir, int num_layers, int h
 int ffn_quantized_ffn_layer(const FfnQuantizedFfn *handle, int layer, FfnMlpWeights *w);
 int ffn_quantized_ffn_free(FfnQuantizedFfn *handle);
 
+/* Replaces the reference's offline converter (scripts/quantize_weights.py:155-325, `convert`): reads the
+ * BF16 safetensors shards of `model_dir` and the model descriptor (its num_layers, layer_ffns,
+ * role_names and role_templates), quantizes the requested roles (NULL / 0 = mlpGate, mlpUp, mlpDown) of
+ * every layer whose feed-forward is "dense" on the GPU with ffn_quantize_int4, and writes
+ * `out_dir/weights.manifest.json` plus `out_dir/artifacts/<role>_layer<L>.{packed,scales}` and the
+ * gate||up pair `mlpGateUp_layer<L>.*` (byte concatenation of its members), with the precision map,
+ * the source files' sizes and digests (taken before and compared after), the descriptor's digest and
+ * the quantization error against the source values.  The manifest is encoded as Python's
+ * json.dump(indent=2, sort_keys=True) encodes it and is what ffn_quant_manifest_parse and the
+ * reference's quant_manifest_parse accept; the artifacts are byte-identical to the reference
+ * converter's.  limit_layers < 0 converts every layer, otherwise layers [0, limit_layers) as the
+ * reference's --limit-layers does.  Refusals with the reference's wording: a non-BF16 source, a
+ * tensor that is not 2-D, a tensor missing from the checkpoint or present in two shards, a
+ * descriptor whose role names and templates differ, a source that changed during conversion, and
+ * whatever the quantizer refuses. */
+int ffn_convert_checkpoint(const char *model_dir, const char *descriptor_path, const char *out_dir,
+                           const char *const *roles, int num_roles, int limit_layers);
+
+/* The converter's JSON encoder by itself: parses a document of numbers, strings, arrays and objects
+ * and writes it back as json.dumps(indent=2, sort_keys=True) would (no trailing newline).  Exists so
+ * the encoding can be compared with Python's without running a conversion; no counterpart in the
+ * reference. */
+int ffn_json_reencode(const char *json_in, char *out, size_t out_bytes);
+
 /* ------------------------------------------------------------------------------------------- */
 /* The reference's kernel test bridge (tests/kernels/kernel_bridge.cu), same names and           */
 /* signatures, so the reference's own gate scripts can be pointed at this library.  Synchronous. */
