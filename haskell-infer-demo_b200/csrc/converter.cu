@@ -398,6 +398,8 @@ static JOut artifact_json(const std::string &file, const char *dtype, const std:
 
 }  // namespace ffn
 
+static const char kFormatArithmetic[] = "csrc/linear_weight.cpp (the Q0 reference)";
+
 using namespace ffn;
 
 extern "C" int ffn_convert_checkpoint(const char *model_dir, const char *descriptor_path, const char *out_dir,
@@ -560,7 +562,7 @@ extern "C" int ffn_convert_checkpoint(const char *model_dir, const char *descrip
     format["packed_dtype"] = JOut::str("u8");
     format["scale_dtype"] = JOut::str("bf16");
     format["packing"] = JOut::str("two_twos_complement_nibbles_per_byte_lower_k_index_in_low_nibble");
-    format["arithmetic"] = JOut::str("libffn_int4 ffn_quantize_int4 (byte-identical to csrc/linear_weight.cpp)");
+    format["arithmetic"] = JOut::str(kFormatArithmetic); /* the definition followed; the reference's --verify compares it */
     doc["format"] = format;
     JOut converter = JOut::obj();
     converter["name"] = JOut::str("libffn_int4 ffn_convert_checkpoint");
@@ -596,6 +598,226 @@ extern "C" int ffn_convert_checkpoint(const char *model_dir, const char *descrip
     if (!write_whole_file(root + "/weights.manifest.json", text.data(), text.size()))
         return fail(FFN_ERR_WEIGHTS, "ffn_convert_checkpoint: cannot write %s/weights.manifest.json", out_dir);
     return FFN_OK;
+}
+
+/* ------------------------------------------------------------------------------------------- */
+/* Verification: re-derive what the manifest claims (scripts/quantize_weights.py:328-461, `verify`) */
+/* ------------------------------------------------------------------------------------------- */
+namespace ffn {
+
+static std::string key_text(long long layer, const std::string &role) { /* Python's repr of (layer, role) */
+    return "(" + std::to_string(layer) + ", '" + role + "')";
+}
+static bool file_exists(const std::string &path) {
+    struct stat st;
+    return stat(path.c_str(), &st) == 0 && S_ISREG(st.st_mode);
+}
+static long long file_size(const std::string &path) {
+    struct stat st;
+    return stat(path.c_str(), &st) == 0 ? (long long)st.st_size : -1;
+}
+static std::string jstr(const Json *j, const char *key) {
+    const Json *v = j ? j->get(key) : nullptr;
+    return v && v->kind == Json::Str ? v->s : std::string();
+}
+static long long jint(const Json *j, const char *key, long long missing = -1) {
+    const Json *v = j ? j->get(key) : nullptr;
+    return v && v->kind == Json::Int ? v->i : missing;
+}
+static std::string dirname_of(const std::string &path) {
+    const size_t slash = path.find_last_of('/');
+    return slash == std::string::npos ? "." : path.substr(0, slash);
+}
+
+}  // namespace ffn
+
+extern "C" int ffn_verify_sidecar(const char *manifest_path, int rederive_samples, char *report, size_t report_bytes) {
+    clear_error();
+    if (!manifest_path || (report_bytes && !report)) return fail(FFN_ERR_CONFIG, "ffn_verify_sidecar: null argument");
+    std::vector<uint8_t> raw;
+    if (!read_whole_file(manifest_path, raw)) return fail(FFN_ERR_WEIGHTS, "ffn_verify_sidecar: cannot read %s", manifest_path);
+    const std::string text(raw.begin(), raw.end());
+    JsonReader reader(text.c_str());
+    Json doc;
+    if (!reader.value(doc) || doc.kind != Json::Obj) return fail(FFN_ERR_WEIGHTS, "ffn_verify_sidecar: %s is not a JSON object", manifest_path);
+    std::vector<std::string> problems;
+    auto require = [&](bool ok, const std::string &message) { if (!ok) problems.push_back(message); };
+
+    require(jint(&doc, "manifest_version") == 1, "unknown manifest version " + std::to_string(jint(&doc, "manifest_version")));
+    const Json *fmt = doc.get("format");
+    const std::pair<const char *, long long> ints[] = {{"abi_version", 1}, {"group", FFN_INT4_GROUP}, {"qmin", -7}, {"qmax", 7},
+                                                       {"invalid_code", -8}, {"zero_point", 0}};
+    for (const auto &kv : ints)
+        require(jint(fmt, kv.first, -99) == kv.second, std::string("the format's ") + kv.first + " is " +
+                std::to_string(jint(fmt, kv.first, -99)) + ", expected " + std::to_string(kv.second));
+    const std::pair<const char *, const char *> strs[] = {
+        {"name", "int4_symmetric_group_bf16_scale"}, {"packed_dtype", "u8"}, {"scale_dtype", "bf16"},
+        {"packing", "two_twos_complement_nibbles_per_byte_lower_k_index_in_low_nibble"}, {"arithmetic", kFormatArithmetic}};
+    for (const auto &kv : strs)
+        require(jstr(fmt, kv.first) == kv.second, std::string("the format's ") + kv.first + " is " + jstr(fmt, kv.first) +
+                ", expected " + kv.second);
+
+    const std::string out_dir = dirname_of(absolute_path(manifest_path));
+    const Json *source = doc.get("source");
+    const std::string source_dir = jstr(source, "model_dir");
+    const Json *files = source ? source->get("files") : nullptr;
+    if (files && files->kind == Json::Arr)
+        for (const Json &rec : files->a) {
+            const std::string name = jstr(&rec, "name"), path = source_dir + "/" + name;
+            require(file_exists(path), "the source file " + name + " is gone");
+            if (file_exists(path)) {
+                long long bytes = 0;
+                std::string hex;
+                require(hash_file(path, &bytes, &hex) && hex == jstr(&rec, "sha256"),
+                        "the source file " + name + " no longer matches its checksum");
+            }
+        }
+
+    /* ---- entries: shapes the format admits, artifacts present, sized and hashed as recorded */
+    const Json *entries = doc.get("entries");
+    if (!entries || entries->kind != Json::Arr) return fail(FFN_ERR_WEIGHTS, "ffn_verify_sidecar: the manifest has no entries array");
+    std::map<std::pair<long long, std::string>, const Json *> by_key;
+    for (const Json &e : entries->a) {
+        const long long layer = jint(&e, "layer");
+        const std::string role = jstr(&e, "role"), key = key_text(layer, role);
+        require(!by_key.count({layer, role}), key + " appears twice");
+        by_key[{layer, role}] = &e;
+        const Json *shape = e.get("logical_shape");
+        long long n = 0, k = 0;
+        if (shape && shape->kind == Json::Arr && shape->a.size() == 2) { n = shape->a[0].i; k = shape->a[1].i; }
+        require(n > 0 && k > 0 && n % 8 == 0 && k % FFN_INT4_GROUP == 0,
+                key + " has a shape the format does not admit: " + std::to_string(n) + "x" + std::to_string(k));
+        const Json *pa = e.get("packed"), *sa = e.get("scales");
+        const std::string packed = out_dir + "/" + jstr(pa, "file"), scales = out_dir + "/" + jstr(sa, "file");
+        require(file_exists(packed), key + " has no payload at " + jstr(pa, "file"));
+        require(file_exists(scales), key + " has no scales at " + jstr(sa, "file"));
+        long long bytes = 0;
+        std::string hex;
+        if (file_exists(packed)) {
+            require(file_size(packed) == n * k / 2, key + " packs to " + std::to_string(file_size(packed)) + " bytes, expected " +
+                    std::to_string(n * k / 2));
+            require(hash_file(packed, &bytes, &hex) && hex == jstr(pa, "sha256"), key + " payload does not match its checksum");
+        }
+        if (file_exists(scales)) {
+            const long long expected = 2 * n * (k / FFN_INT4_GROUP);
+            require(file_size(scales) == expected, key + " scales are " + std::to_string(file_size(scales)) + " bytes, expected " +
+                    std::to_string(expected));
+            require(hash_file(scales, &bytes, &hex) && hex == jstr(sa, "sha256"), key + " scales do not match their checksum");
+        }
+    }
+
+    /* ---- the precision map covers every role of every layer once and agrees with the entries */
+    const Json *dj = doc.get("descriptor");
+    const std::string desc_path = jstr(dj, "path");
+    std::vector<uint8_t> desc_raw;
+    Json desc;
+    size_t covered_cells = 0;
+    if (!read_whole_file(desc_path, desc_raw)) {
+        problems.push_back("the descriptor " + desc_path + " cannot be read");
+    } else {
+        require(sha_hex_of(desc_raw.data(), desc_raw.size()) == jstr(dj, "sha256"), "the descriptor no longer matches its checksum");
+        const std::string desc_text(desc_raw.begin(), desc_raw.end());
+        JsonReader dreader(desc_text.c_str());
+        if (!dreader.value(desc) || desc.kind != Json::Obj) problems.push_back("the descriptor is not a JSON object");
+    }
+    std::map<std::pair<long long, std::string>, bool> covered;
+    const Json *pmap = doc.get("precision_map");
+    if (pmap && pmap->kind == Json::Arr)
+        for (const Json &rec : pmap->a) {
+            const long long layer = jint(&rec, "layer");
+            const std::string role = jstr(&rec, "role"), key = key_text(layer, role);
+            require(!covered.count({layer, role}), "the precision map lists " + key + " twice");
+            covered[{layer, role}] = true;
+            require((jstr(&rec, "precision") == "int4") == (by_key.count({layer, role}) != 0),
+                    "the precision map and the entries disagree about " + key);
+        }
+    covered_cells = covered.size();
+    const Json *names = desc.get("role_names");
+    if (names && names->kind == Json::Arr)
+        for (long long layer = 0; layer < jint(&desc, "num_layers", 0); ++layer)
+            for (const Json &name : names->a)
+                require(covered.count({layer, name.s}) != 0, "the precision map does not cover layer " + std::to_string(layer) + "'s " + name.s);
+
+    /* ---- each pair is exactly its members' bytes, in the order the rule names */
+    const Json *pairs = doc.get("pairs");
+    size_t pair_count = 0;
+    if (pairs && pairs->kind == Json::Arr)
+        for (const Json &pair : pairs->a) {
+            ++pair_count;
+            const long long layer = jint(&pair, "layer");
+            const Json *members = pair.get("members");
+            std::vector<const Json *> found;
+            bool missing_member = !members || members->kind != Json::Arr;
+            if (!missing_member)
+                for (const Json &m : members->a) {
+                    const auto it = by_key.find({layer, jstr(&m, "role")});
+                    if (it == by_key.end()) missing_member = true; else found.push_back(it->second);
+                }
+            if (missing_member) { problems.push_back("pair at layer " + std::to_string(layer) + " names a member that has no entry"); continue; }
+            std::vector<uint8_t> want_packed, want_scales, got_packed, got_scales, part;
+            bool all_there = read_whole_file(out_dir + "/" + jstr(pair.get("packed"), "file"), got_packed) &&
+                             read_whole_file(out_dir + "/" + jstr(pair.get("scales"), "file"), got_scales);
+            long long rows = 0, k = 0;
+            for (const Json *m : found) {
+                all_there = all_there && read_whole_file(out_dir + "/" + jstr(m->get("packed"), "file"), part);
+                want_packed.insert(want_packed.end(), part.begin(), part.end());
+                all_there = all_there && read_whole_file(out_dir + "/" + jstr(m->get("scales"), "file"), part);
+                want_scales.insert(want_scales.end(), part.begin(), part.end());
+                const Json *shape = m->get("logical_shape");
+                if (shape && shape->kind == Json::Arr && shape->a.size() == 2) { rows += shape->a[0].i; if (!k) k = shape->a[1].i; }
+            }
+            if (!all_there) { problems.push_back("pair at layer " + std::to_string(layer) + " is missing an artifact"); continue; }
+            require(got_packed == want_packed, "pair at layer " + std::to_string(layer) + " is not its members' packed rows in order");
+            require(got_scales == want_scales, "pair at layer " + std::to_string(layer) + " is not its members' scale rows in order");
+            const Json *shape = pair.get("logical_shape");
+            const bool shape_ok = shape && shape->kind == Json::Arr && shape->a.size() == 2 && shape->a[0].i == rows && shape->a[1].i == k;
+            require(shape_ok, "pair at layer " + std::to_string(layer) + " claims another shape than [" + std::to_string(rows) + ", " +
+                    std::to_string(k) + "]");
+        }
+
+    /* ---- a sample of entries must re-derive from the source checkpoint, on the GPU */
+    if (rederive_samples > 0 && !entries->a.empty()) {
+        std::vector<std::string> shards;
+        std::map<std::string, TensorInfo> index;
+        int st = index_checkpoint(source_dir.c_str(), shards, index);
+        if (st) return st;
+        DeviceBuffers dev;
+        ErrorStats unused;
+        std::vector<float> src;
+        std::vector<uint8_t> packed, scales, on_disk;
+        for (size_t e = 0; e < entries->a.size() && e < (size_t)rederive_samples; ++e) {
+            const Json &entry = entries->a[e];
+            const std::string packed_path = out_dir + "/" + jstr(entry.get("packed"), "file");
+            const std::string scales_path = out_dir + "/" + jstr(entry.get("scales"), "file");
+            if (!file_exists(packed_path) || !file_exists(scales_path)) continue; /* already reported above */
+            const std::string tensor = jstr(&entry, "checkpoint_tensor");
+            const auto it = index.find(tensor);
+            if (it == index.end()) { problems.push_back(tensor + " is not in the source checkpoint"); continue; }
+            st = read_tensor_f32(tensor, it->second, src);
+            if (st) return st;
+            st = quantize_tensor(dev, src, it->second.shape[0], it->second.shape[1], packed, scales, unused);
+            if (st) return st;
+            const std::string label = jstr(&entry, "role") + "_" + std::to_string(jint(&entry, "layer"));
+            require(read_whole_file(packed_path, on_disk) && on_disk == packed, label + " does not re-derive from the source");
+            require(read_whole_file(scales_path, on_disk) && on_disk == scales, label + " scales do not re-derive from the source");
+        }
+    }
+
+    std::string out;
+    if (problems.empty()) {
+        out = "verify: " + std::to_string(entries->a.size()) + " entries, " + std::to_string(pair_count) +
+              " pair(s) match their members' rows, the precision map covers " + std::to_string(covered_cells) +
+              " (role, layer) cells, the source is unchanged" +
+              (rederive_samples > 0 ? " and the sampled artifacts re-derive from it" : "") + "\n";
+    } else {
+        for (const std::string &p : problems) out += "verify: " + p + "\n";
+    }
+    if (report_bytes) {
+        const size_t n = out.size() < report_bytes - 1 ? out.size() : report_bytes - 1;
+        memcpy(report, out.data(), n);
+        report[n] = '\0';
+    }
+    return (int)problems.size();
 }
 
 /* The encoder by itself, for the test that compares it with Python's json.dumps(indent=2, sort_keys=True):

@@ -90,6 +90,7 @@ def _declare(lib):
         "ffn_int4_describe_plan": [ci, ci, ci, ci, ci, ctypes.c_char_p, ctypes.c_size_t],
         "ffn_convert_checkpoint": [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_char_p), ci, ci],
         "ffn_json_reencode": [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_size_t],
+        "ffn_verify_sidecar": [ctypes.c_char_p, ci, ctypes.c_char_p, ctypes.c_size_t],
     }
     lib.ffn_quant_manifest_free.argtypes = [vp]
     lib.ffn_quant_manifest_free.restype = None

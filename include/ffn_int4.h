@@ -333,6 +333,18 @@ int ffn_quantized_ffn_free(FfnQuantizedFfn *handle);
 int ffn_convert_checkpoint(const char *model_dir, const char *descriptor_path, const char *out_dir,
                            const char *const *roles, int num_roles, int limit_layers);
 
+/* Replaces the reference converter's --verify mode (scripts/quantize_weights.py:328-461): re-derives what
+ * a manifest claims instead of trusting it.  Checks, in the reference's order and with its wording:
+ * manifest version and the frozen format block; the source files still exist and hash as recorded;
+ * no (layer, role) twice; shapes the format admits; every artifact present, of the recorded size and
+ * digest; the descriptor's digest; the precision map covers every role of every layer exactly once
+ * and agrees with the entries; every pair is its members' bytes in order and claims their combined
+ * shape; and, when rederive_samples > 0, the first that many entries re-quantized from the source
+ * checkpoint on the GPU are byte-identical to the artifacts (the reference samples two).  Returns the
+ * number of problems found (0 = verified) or a negative status when the manifest cannot be read at
+ * all; `report` receives one "verify: ..." line per problem, or the summary line. */
+int ffn_verify_sidecar(const char *manifest_path, int rederive_samples, char *report, size_t report_bytes);
+
 /* The converter's JSON encoder by itself: parses a document of numbers, strings, arrays and objects
  * and writes it back as json.dumps(indent=2, sort_keys=True) would (no trailing newline).  Exists so
  * the encoding can be compared with Python's without running a conversion; no counterpart in the
