@@ -164,3 +164,32 @@ def test_unrepresentable_group_is_refused_with_the_quantizers_message(cuda, tmp_
     st, msg = convert(bd, desc, tmp_path / "out")
     assert st == -3 and "row 5 group 1" in msg
     assert not os.path.exists(tmp_path / "out" / "weights.manifest.json")
+
+
+def test_verify_rederives_from_the_source(cuda, tmp_path):
+    """The converter's output passes ffn_verify_sidecar including the re-derivation of sampled entries
+    from the source checkpoint; an artifact altered together with its recorded digest passes every
+    host check and is caught only by that re-derivation."""
+    from test_verify_sidecar_cpu import verify
+    d, desc, _ = model(tmp_path, layers=1)
+    out = str(tmp_path / "out")
+    st, msg = convert(d, desc, out)
+    assert st == 0, msg
+    n, report = verify(out, samples=2)
+    assert n == 0, report
+    assert report.endswith("the source is unchanged and the sampled artifacts re-derive from it\n")
+
+    path = os.path.join(out, "artifacts", "mlpGate_layer0.packed")
+    raw = bytearray(open(path, "rb").read())
+    raw[3] ^= 0x01
+    open(path, "wb").write(bytes(raw))
+    manifest_path = os.path.join(out, "weights.manifest.json")
+    doc = json.load(open(manifest_path))
+    doc["entries"][0]["packed"]["sha256"] = sha(bytes(raw))
+    assert doc["entries"][0]["role"] == "mlpGate"
+    with open(manifest_path, "w") as f:
+        f.write(json.dumps(doc, indent=2, sort_keys=True) + "\n")
+    n, report = verify(out, samples=2)
+    assert "verify: mlpGate_0 does not re-derive from the source\n" in report
+    assert "verify: pair at layer 0 is not its members' packed rows in order\n" in report
+    assert n == 2, report
