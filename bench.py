@@ -206,7 +206,17 @@ def run_ours(args):
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps, times = 5, []
+    # One more untimed replay tells how many timed replays make the region long enough (about 0.6 s) for the
+    # clock sampler to see it several times; every rank must agree on the count.
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        graph.replay()
+        e1.record(stream)
+    barrier()
+    est = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(est, op=dist.ReduceOp.MAX)
+    reps, times = int(min(400, max(5, -(-600.0 // max(float(est.item()), 1e-3))))), []
     for _ in range(reps):
         barrier()
         with torch.cuda.stream(stream):
