@@ -355,6 +355,11 @@ def run_reference(args):
         assert st == 0
         return out
 
+    # all the host threads this process may use, also when a launcher set OMP_NUM_THREADS=1 for its children
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except (AttributeError, OSError):
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
     xt = torch.from_numpy(x)
 
     def step():
