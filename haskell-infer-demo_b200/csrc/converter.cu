@@ -23,6 +23,7 @@
 #include <sys/stat.h>
 
 #include <algorithm>
+#include <charconv>
 #include <map>
 #include <memory>
 #include <string>
@@ -59,11 +60,10 @@ static std::string py_float_repr(double v) {
     if (isinf(v)) return v > 0 ? "Infinity" : "-Infinity";
     if (v == 0.0) return signbit(v) ? "-0.0" : "0.0";
     char buf[64];
-    int prec = 1;
-    for (; prec <= 17; ++prec) {
-        snprintf(buf, sizeof(buf), "%.*e", prec - 1, v);
-        if (strtod(buf, nullptr) == v) break;
-    }
+    /* shortest digits that read back as v, and among those the closest to v: std::to_chars guarantees both
+     * (trying printf precisions does not: near a power of two the rounded candidate can miss) */
+    const std::to_chars_result r = std::to_chars(buf, buf + sizeof(buf) - 1, v, std::chars_format::scientific);
+    *r.ptr = '\0';
     /* buf = [-]d[.ddd]e[+-]XX */
     std::string text(buf);
     const bool neg = text[0] == '-';

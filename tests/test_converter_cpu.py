@@ -25,7 +25,7 @@ def reencode(doc):
 def test_encoder_matches_python():
     rng = np.random.default_rng(7)
     floats = [0.0, 1.0, -1.5, 0.1, 1e-5, 1.5e-5, 0.0001, 0.00012345, 123456789.125, 1e15, 1e16, 1.2345e16, 1e22, 5e-324,
-              1.7976931348623157e308, 2.0 ** -20, 1 / 3, 0.004241943359375, float(np.float32(0.0032958984)),
+              1.7976931348623157e308, 2.0 ** -20, 2.0 ** -24, 2.0 ** -1074, 2.0 ** 70, 1 / 3, 0.004241943359375, float(np.float32(0.0032958984)),
               float(np.float32(1.1920929e-07))]
     floats += [float(x) for x in rng.standard_normal(200) * 10.0 ** rng.integers(-12, 12, 200)]
     floats += [float(np.float32(x)) for x in rng.standard_normal(100) * 1e-3]
@@ -133,3 +133,24 @@ def test_no_cpu_fallback(tmp_path):
     st, msg = convert(d, desc, tmp_path / "out")
     assert st < 0 and msg
     assert not os.path.exists(tmp_path / "out" / "weights.manifest.json")
+
+
+def test_encoder_matches_python_on_random_documents():
+    """Property check (hypothesis): any document of integers, finite floats, text, lists and dictionaries."""
+    from hypothesis import given, settings, strategies as st
+
+    leaves = st.one_of(st.integers(min_value=-(10 ** 15), max_value=10 ** 15),
+                       st.floats(allow_nan=False, allow_infinity=False),
+                       st.text(max_size=12))
+    docs = st.recursive(leaves, lambda kids: st.one_of(st.lists(kids, max_size=4),
+                                                       st.dictionaries(st.text(min_size=1, max_size=6), kids, max_size=4)),
+                        max_leaves=25)
+
+    @settings(max_examples=300, deadline=None)
+    @given(docs)
+    def check(doc):
+        if not isinstance(doc, (list, dict)):
+            doc = [doc]
+        assert reencode(doc) == json.dumps(doc, indent=2, sort_keys=True)
+
+    check()
