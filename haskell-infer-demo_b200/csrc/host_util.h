@@ -83,7 +83,10 @@ struct Sha256 {
 };
 
 /* ------------------------------------------------------------------------------------------- */
-/* A small strict JSON reader (objects refuse duplicate keys; nothing may follow the document)   */
+/* A small strict JSON reader (objects refuse duplicate keys; nothing may follow the document).  */
+/* `manifest_dialect` switches to what the reference's manifest reader accepts at this level      */
+/* (csrc/quant_manifest.c:71-175): duplicate keys are kept for the caller to judge, raw control   */
+/* bytes pass, a number may start with '+', and a \u escape above 0x7F is refused (ASCII schema). */
 /* ------------------------------------------------------------------------------------------- */
 struct Json {
     enum Kind { Null, Bool, Int, Real, Str, Arr, Obj } kind = Null;
@@ -104,6 +107,7 @@ struct JsonReader {
     const char *p, *end;
     std::string error;
     int depth = 0;
+    bool manifest_dialect = false;
     explicit JsonReader(const char *text) : p(text), end(text + strlen(text)) {}
     void ws() { while (p < end && (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r')) ++p; }
     bool fail_at(const char *what) { if (error.empty()) error = std::string("quant manifest: ") + what; return false; }
@@ -113,7 +117,7 @@ struct JsonReader {
         out.clear();
         while (p < end && *p != '"') {
             unsigned char c = (unsigned char)*p++;
-            if (c < 0x20) return fail_at("a control character inside a string");
+            if (c < 0x20 && !manifest_dialect) return fail_at("a control character inside a string");
             if (c == '\\') {
                 if (p >= end) return fail_at("the document ends inside a string");
                 const char e = *p++;
@@ -132,6 +136,7 @@ struct JsonReader {
                         else if (h >= 'A' && h <= 'F') v |= (unsigned)(h - 'A' + 10);
                         else return fail_at("a malformed \\u escape");
                     }
+                    if (manifest_dialect && v > 0x7F) return fail_at("a string outside ASCII (the schema is ASCII-only)");
                     if (v < 0x80) out += (char)v;
                     else if (v < 0x800) { out += (char)(0xC0 | (v >> 6)); out += (char)(0x80 | (v & 0x3F)); }
                     else { out += (char)(0xE0 | (v >> 12)); out += (char)(0x80 | ((v >> 6) & 0x3F)); out += (char)(0x80 | (v & 0x3F)); }
@@ -161,7 +166,7 @@ struct JsonReader {
                     ws();
                     std::string key;
                     if (!string(key)) { ok = false; break; }
-                    if (out.get(key.c_str())) { ok = fail_at(("the key \"" + key + "\" appears twice").c_str()); break; }
+                    if (!manifest_dialect && out.get(key.c_str())) { ok = fail_at(("the key \"" + key + "\" appears twice").c_str()); break; }
                     ws();
                     if (p >= end || *p != ':') { ok = fail_at("':' was expected"); break; }
                     ++p;
@@ -197,10 +202,10 @@ struct JsonReader {
         else if (!strncmp(p, "null", 4)) { out.kind = Json::Null; p += 4; }
         else {
             const char *start = p;
-            if (p < end && *p == '-') ++p;
+            if (p < end && (*p == '-' || (manifest_dialect && *p == '+'))) ++p;
             bool digits = false, real = false;
             while (p < end && *p >= '0' && *p <= '9') { ++p; digits = true; }
-            if (p < end && *p == '.') { real = true; ++p; while (p < end && *p >= '0' && *p <= '9') ++p; }
+            if (p < end && *p == '.') { real = true; ++p; while (p < end && *p >= '0' && *p <= '9') { ++p; digits = true; } }
             if (p < end && (*p == 'e' || *p == 'E')) {
                 real = true; ++p;
                 if (p < end && (*p == '+' || *p == '-')) ++p;

@@ -79,15 +79,41 @@ static int qfail(int status, const char *fmt, ...) {
     return status;
 }
 
-static bool as_int(const Json *j, long long *out) {
-    if (!j || j->kind != Json::Int) return false;
-    *out = j->i;
-    return true;
+/* ---- the reader walks the parsed document in document order and applies each check where the
+ * reference's streaming reader applies it (csrc/quant_manifest.c:277-1063), so that a document with
+ * one fault gets the reference's status: wrong type or missing field = SYNTAX, a string that would
+ * not fit the reference's fixed buffers = ARG, disagreement with the frozen format = FORMAT,
+ * disagreement between extents = SHAPE. ---- */
+constexpr size_t kNameMax = 64, kPathMax = 512, kShaMax = 65; /* csrc/include/quant_manifest.h:47-51 */
+
+static int need_str(const Json &j, size_t buffer, std::string *out, const char *what) {
+    if (j.kind != Json::Str) return qfail(QM_SYNTAX, "quant manifest: %s is not a string", what);
+    if (j.s.size() + 1 > buffer) return qfail(QM_ARG, "quant manifest: %s does not fit %zu bytes", what, buffer);
+    *out = j.s;
+    return QM_OK;
 }
-static bool as_str(const Json *j, std::string *out) {
-    if (!j || j->kind != Json::Str) return false;
-    *out = j->s;
-    return true;
+static int need_int(const Json &j, long long *out, const char *what) {
+    if (j.kind == Json::Int) { *out = j.i; return QM_OK; }
+    if (j.kind == Json::Real && j.d >= -9.0e18 && j.d <= 9.0e18 && (double)(long long)j.d == j.d) { *out = (long long)j.d; return QM_OK; }
+    return qfail(QM_SYNTAX, "quant manifest: %s is not an integer", what);
+}
+static int need_key(const std::string &key) {
+    if (key.size() + 1 > kNameMax) return qfail(QM_ARG, "quant manifest: a key does not fit %zu bytes", kNameMax);
+    return QM_OK;
+}
+/* a value the schema does not use: anything well-formed, within the reference's scratch sizes and depth */
+static int skipped(const Json &j, int depth) {
+    if (depth > 32) return qfail(QM_SYNTAX, "quant manifest: nesting is too deep");
+    if (j.kind == Json::Str && j.s.size() + 1 > kPathMax) return qfail(QM_ARG, "quant manifest: a string does not fit %zu bytes", kPathMax);
+    if (j.kind == Json::Arr)
+        for (const Json &e : j.a) { const int st = skipped(e, depth + 1); if (st) return st; }
+    if (j.kind == Json::Obj)
+        for (const auto &kv : j.o) {
+            if (kv.first.size() + 1 > kPathMax) return qfail(QM_ARG, "quant manifest: a key does not fit %zu bytes", kPathMax);
+            const int st = skipped(kv.second, depth + 1);
+            if (st) return st;
+        }
+    return QM_OK;
 }
 
 static bool is_sha256_hex(const std::string &s) {
@@ -97,27 +123,41 @@ static bool is_sha256_hex(const std::string &s) {
     return true;
 }
 
-/* One artifact object.  `is_scales` artifacts carry a count; packed ones do not. */
-static int read_artifact(const Json *j, Artifact *a, const char *want_dtype, const char *where, bool is_scales) {
-    if (!j || j->kind != Json::Obj) return qfail(QM_SYNTAX, "quant manifest: %s has no %s artifact", where, is_scales ? "scales" : "packed");
-    long long bytes = -1, count = -1;
-    if (!as_str(j->get("file"), &a->file) || a->file.empty() || !as_str(j->get("dtype"), &a->dtype) ||
-        !as_str(j->get("sha256"), &a->sha256) || !as_int(j->get("bytes"), &bytes))
-        return qfail(QM_SYNTAX, "quant manifest: %s has an incomplete %s artifact", where, is_scales ? "scales" : "packed");
-    if (is_scales && !as_int(j->get("count"), &count))
-        return qfail(QM_SYNTAX, "quant manifest: %s's scales record no count", where);
-    a->bytes = bytes;
-    a->count = is_scales ? count : -1;
-    if (a->dtype != want_dtype)
-        return qfail(QM_FORMAT, "quant manifest: %s's %s artifact is %s, the format stores %s", where,
-                     is_scales ? "scales" : "packed", a->dtype.c_str(), want_dtype);
-    if (!is_sha256_hex(a->sha256))
-        return qfail(QM_FORMAT, "quant manifest: %s's %s digest is not 64 lower-case hex digits", where,
-                     is_scales ? "scales" : "packed");
-    if (a->bytes < 0 || (is_scales && a->count < 0))
-        return qfail(QM_SHAPE, "quant manifest: %s records a negative extent", where);
-    if (a->file.size() >= 512 || a->file[0] == '/' || a->file.find("..") != std::string::npos)
-        return qfail(QM_FORMAT, "quant manifest: %s names an artifact outside the sidecar directory", where);
+/* One artifact object as written; `has_count` artifacts (scales) must carry a count, payloads must not. */
+static int read_artifact(const Json &j, Artifact *a, bool has_count) {
+    if (j.kind != Json::Obj) return qfail(QM_SYNTAX, "quant manifest: an artifact is not an object");
+    if (j.o.empty()) return qfail(QM_SYNTAX, "quant manifest: an artifact object is empty");
+    bool seen_bytes = false, seen_count = false, seen_dtype = false, seen_file = false, seen_sha = false;
+    a->count = -1;
+    for (const auto &kv : j.o) {
+        int st = need_key(kv.first);
+        if (st) return st;
+        bool *seen = kv.first == "bytes" ? &seen_bytes : kv.first == "count" ? &seen_count : kv.first == "dtype" ? &seen_dtype
+                   : kv.first == "file" ? &seen_file : kv.first == "sha256" ? &seen_sha : nullptr;
+        if (!seen) { if ((st = skipped(kv.second, 0))) return st; continue; }
+        if (*seen) return qfail(QM_SYNTAX, "quant manifest: \"%s\" appears twice in an artifact", kv.first.c_str());
+        *seen = true;
+        if (seen == &seen_bytes) st = need_int(kv.second, &a->bytes, "an artifact's bytes");
+        else if (seen == &seen_count) st = need_int(kv.second, &a->count, "an artifact's count");
+        else if (seen == &seen_dtype) st = need_str(kv.second, kNameMax, &a->dtype, "an artifact's dtype");
+        else if (seen == &seen_file) st = need_str(kv.second, kPathMax, &a->file, "an artifact's file");
+        else st = need_str(kv.second, kShaMax, &a->sha256, "an artifact's sha256");
+        if (st) return st;
+    }
+    if (!seen_bytes || !seen_dtype || !seen_file || !seen_sha) return qfail(QM_SYNTAX, "quant manifest: an artifact lacks one of bytes/dtype/file/sha256");
+    if (has_count && !seen_count) return qfail(QM_SYNTAX, "quant manifest: a scale artifact has no count");
+    if (!has_count && seen_count) return qfail(QM_SYNTAX, "quant manifest: a packed payload carries a count");
+    return QM_OK;
+}
+
+/* ... and against the frozen format (require_artifact, csrc/quant_manifest.c:341-364, in its order) */
+static int check_artifact(const Artifact &a, const char *want_dtype, const char *where, bool is_scales) {
+    const char *kind = is_scales ? "scales" : "packed";
+    if (!is_sha256_hex(a.sha256)) return qfail(QM_FORMAT, "quant manifest: %s's %s digest is not 64 lower-case hex digits", where, kind);
+    if (a.bytes <= 0) return qfail(QM_FORMAT, "quant manifest: %s's %s artifact has a nonpositive byte count", where, kind);
+    if (a.file.empty()) return qfail(QM_FORMAT, "quant manifest: %s's %s artifact names no file", where, kind);
+    if (a.dtype != want_dtype) return qfail(QM_FORMAT, "quant manifest: %s's %s artifact is %s, the format stores %s", where, kind, a.dtype.c_str(), want_dtype);
+    if (is_scales != (a.count >= 0)) return qfail(QM_FORMAT, "quant manifest: %s's %s artifact %s a scale count", where, kind, is_scales ? "is missing" : "carries");
     return QM_OK;
 }
 
@@ -132,11 +172,11 @@ static int layout_of(long long n, long long k, long long group, long long *packe
     return QM_OK;
 }
 
-static int read_shape(const Json *j, long long *n, long long *k) {
-    if (!j || j->kind != Json::Arr || j->a.size() != 2 || j->a[0].kind != Json::Int || j->a[1].kind != Json::Int) return 0;
-    *n = j->a[0].i;
-    *k = j->a[1].i;
-    return 1;
+static int read_shape(const Json &j, long long *n, long long *k) {
+    if (j.kind != Json::Arr || j.a.size() != 2) return qfail(QM_SYNTAX, "quant manifest: a shape is not a list of two integers");
+    int st = need_int(j.a[0], n, "a shape's rows");
+    if (!st) st = need_int(j.a[1], k, "a shape's columns");
+    return st;
 }
 
 static int find_entry(const Manifest &m, int layer, const char *role) {
@@ -150,69 +190,80 @@ static int find_pair(const Manifest &m, const char *name, int layer) {
     return -1;
 }
 
-static int parse_manifest(const char *text, Manifest *m) {
-    if (!text || !m) return qfail(QM_ARG, "quant manifest: null argument");
-    JsonReader reader(text);
-    Json root;
-    reader.ws();
-    if (reader.p >= reader.end) return qfail(QM_SYNTAX, "quant manifest: the document is empty");
-    if (!reader.value(root)) return qfail(QM_SYNTAX, "%s", reader.error.c_str());
-    reader.ws();
-    if (reader.p != reader.end) return qfail(QM_SYNTAX, "quant manifest: bytes follow the document");
-    if (root.kind != Json::Obj) return qfail(QM_SYNTAX, "quant manifest: the document is not an object");
-    const Json *format = root.get("format"), *entries = root.get("entries"), *pairs = root.get("pairs"),
-               *precision = root.get("precision_map"), *converter = root.get("converter"), *source = root.get("source");
-    long long version = 0;
-    if (!as_int(root.get("manifest_version"), &version) || !format || format->kind != Json::Obj || !entries ||
-        entries->kind != Json::Arr || !pairs || pairs->kind != Json::Arr || !precision || precision->kind != Json::Arr)
-        return qfail(QM_SYNTAX, "quant manifest: a required section (manifest_version, format, entries, pairs, precision_map) is missing");
-    if (version != 1) return qfail(QM_FORMAT, "quant manifest: manifest_version %lld, this reader speaks 1", version);
-    m->manifest_version = (int)version;
-
-    /* the format block has to be the frozen format (csrc/include/linear_weight.h:46-54) */
-    long long abi = 0, group = 0, qmin = 0, qmax = 0, zp = 0, invalid = 0;
-    if (!as_int(format->get("abi_version"), &abi) || !as_int(format->get("group"), &group) || !as_int(format->get("qmin"), &qmin) ||
-        !as_int(format->get("qmax"), &qmax) || !as_int(format->get("zero_point"), &zp) || !as_int(format->get("invalid_code"), &invalid) ||
-        !as_str(format->get("packed_dtype"), &m->packed_dtype) || !as_str(format->get("scale_dtype"), &m->scale_dtype))
-        return qfail(QM_SYNTAX, "quant manifest: the format block is incomplete");
-    if (abi != 1) return qfail(QM_FORMAT, "quant manifest: format abi_version %lld, this reader speaks 1", abi);
-    if (group != FFN_INT4_GROUP || qmin != -7 || qmax != 7 || zp != 0 || invalid != -8)
+static int read_format(const Json &j, Manifest *m) {
+    if (j.kind != Json::Obj || j.o.empty()) return qfail(QM_SYNTAX, "quant manifest: the format block is not a filled object");
+    bool seen[9] = {};
+    static const char *const kInts[] = {"abi_version", "group", "qmin", "qmax", "zero_point", "invalid_code"};
+    long long iv[6] = {};
+    std::string name;
+    for (const auto &kv : j.o) {
+        int st = need_key(kv.first);
+        if (st) return st;
+        int which = -1;
+        for (int i = 0; i < 6; ++i) if (kv.first == kInts[i]) which = i;
+        if (which >= 0) { seen[which] = true; st = need_int(kv.second, &iv[which], kInts[which]); }
+        else if (kv.first == "name") { seen[6] = true; st = need_str(kv.second, kNameMax, &name, "the format's name"); }
+        else if (kv.first == "packed_dtype") { seen[7] = true; st = need_str(kv.second, kNameMax, &m->packed_dtype, "packed_dtype"); }
+        else if (kv.first == "scale_dtype") { seen[8] = true; st = need_str(kv.second, kNameMax, &m->scale_dtype, "scale_dtype"); }
+        else st = skipped(kv.second, 0);
+        if (st) return st;
+    }
+    for (bool b : seen) if (!b) return qfail(QM_SYNTAX, "quant manifest: the format block is incomplete");
+    if (iv[0] != 1) return qfail(QM_FORMAT, "quant manifest: format abi_version %lld, this reader speaks 1", iv[0]);
+    if (iv[1] != FFN_INT4_GROUP || iv[2] != -7 || iv[3] != 7 || iv[4] != 0 || iv[5] != -8)
         return qfail(QM_FORMAT, "quant manifest: the format block (group %lld, codes [%lld, %lld], zero point %lld, reserved %lld) "
-                     "is not the frozen format", group, qmin, qmax, zp, invalid);
+                     "is not the frozen format", iv[1], iv[2], iv[3], iv[4], iv[5]);
     if (m->packed_dtype != "u8" || m->scale_dtype != "bf16")
         return qfail(QM_FORMAT, "quant manifest: the format stores %s codes and %s scales, not u8 and bf16",
                      m->packed_dtype.c_str(), m->scale_dtype.c_str());
-    m->format_abi_version = (int)abi; m->group = group; m->qmin = (int)qmin; m->qmax = (int)qmax;
-    m->zero_point = (int)zp; m->invalid_code = (int)invalid;
-    if (converter && converter->kind == Json::Obj) {
-        long long cv = 0;
-        as_str(converter->get("name"), &m->converter_name);
-        if (as_int(converter->get("version"), &cv)) m->converter_version = (int)cv;
-    }
-    if (source && source->kind == Json::Obj) as_str(source->get("model_dir"), &m->source_model_dir);
+    m->format_abi_version = 1; m->group = iv[1]; m->qmin = -7; m->qmax = 7; m->zero_point = 0; m->invalid_code = -8;
+    return QM_OK;
+}
 
-    if (entries->a.size() > (size_t)kMaxEntries) return qfail(QM_SHAPE, "quant manifest: more than %d entries", kMaxEntries);
-    for (const Json &e : entries->a) {
-        if (e.kind != Json::Obj) return qfail(QM_SYNTAX, "quant manifest: an entry is not an object");
+static int read_entries(const Json &arr, Manifest *m) {
+    if (arr.kind != Json::Arr) return qfail(QM_SYNTAX, "quant manifest: entries is not a list");
+    if (arr.a.empty()) return qfail(QM_FORMAT, "quant manifest: entries is empty");
+    for (const Json &e : arr.a) {
+        if (m->entries.size() >= (size_t)kMaxEntries) return qfail(QM_FORMAT, "quant manifest: more than %d entries", kMaxEntries);
+        if (e.kind != Json::Obj || e.o.empty()) return qfail(QM_SYNTAX, "quant manifest: an entry is not a filled object");
         Entry en;
-        long long layer = -1, role_index = -1, group_e = 0;
-        std::string axis;
-        if (!as_str(e.get("role"), &en.role) || !as_int(e.get("layer"), &layer) || !as_int(e.get("group"), &group_e) ||
-            !read_shape(e.get("logical_shape"), &en.n, &en.k))
-            return qfail(QM_SYNTAX, "quant manifest: an entry lacks role, layer, group or logical_shape");
-        if (en.role.empty() || en.role.size() >= 64) return qfail(QM_FORMAT, "quant manifest: an entry has no usable role");
-        if (layer < 0) return qfail(QM_FORMAT, "quant manifest: %s has a negative layer", en.role.c_str());
-        if (as_str(e.get("group_axis"), &axis) && axis != "k")
-            return qfail(QM_FORMAT, "quant manifest: %s groups along %s, the format groups along k", en.role.c_str(), axis.c_str());
-        as_int(e.get("role_index"), &role_index);
-        en.layer = (int)layer; en.role_index = (int)role_index; en.group = group_e;
+        static const char *const kNames[8] = {"role", "role_index", "layer", "logical_shape", "packed", "scales", "group", "group_axis"};
+        bool seen[8] = {};
+        for (const auto &kv : e.o) {
+            int st = need_key(kv.first);
+            if (st) return st;
+            int which = -1;
+            for (int i = 0; i < 8; ++i) if (kv.first == kNames[i]) which = i;
+            if (which < 0) { if ((st = skipped(kv.second, 0))) return st; continue; }
+            if (seen[which]) return qfail(QM_SYNTAX, "quant manifest: \"%s\" appears twice in an entry", kNames[which]);
+            seen[which] = true;
+            long long v = 0;
+            std::string axis;
+            switch (which) {
+                case 0: st = need_str(kv.second, kNameMax, &en.role, "an entry's role"); break;
+                case 1: st = need_int(kv.second, &v, "an entry's role_index"); en.role_index = (int)v; break;
+                case 2: st = need_int(kv.second, &v, "an entry's layer"); en.layer = (int)v; break;
+                case 3: st = read_shape(kv.second, &en.n, &en.k); break;
+                case 4: st = read_artifact(kv.second, &en.packed, false); break;
+                case 5: st = read_artifact(kv.second, &en.scales, true); break;
+                case 6: st = need_int(kv.second, &en.group, "an entry's group"); break;
+                default:
+                    st = need_str(kv.second, kNameMax, &axis, "an entry's group_axis");
+                    if (!st && axis != "k") st = qfail(QM_FORMAT, "quant manifest: an entry groups along %s, the format groups along k", axis.c_str());
+            }
+            if (st) return st;
+        }
+        if (!seen[0] || !seen[2] || !seen[3] || !seen[4] || !seen[5] || !seen[6])
+            return qfail(QM_SYNTAX, "quant manifest: an entry lacks one of role/layer/logical_shape/packed/scales/group");
+        if (en.role.empty()) return qfail(QM_FORMAT, "quant manifest: an entry has no role");
+        if (en.layer < 0) return qfail(QM_FORMAT, "quant manifest: %s has a negative layer", en.role.c_str());
         char where[128];
         snprintf(where, sizeof(where), "%s layer %d", en.role.c_str(), en.layer);
         long long pb = 0, sc = 0;
         int st = layout_of(en.n, en.k, en.group, &pb, &sc, where);
+        if (!st) st = check_artifact(en.packed, "u8", where, false);
+        if (!st) st = check_artifact(en.scales, "bf16", where, true);
         if (st) return st;
-        if ((st = read_artifact(e.get("packed"), &en.packed, "u8", where, false))) return st;
-        if ((st = read_artifact(e.get("scales"), &en.scales, "bf16", where, true))) return st;
         if (en.packed.bytes != pb)
             return qfail(QM_SHAPE, "quant manifest: %s records %lld packed bytes, [%lld, %lld] at group %lld is %lld", where,
                          en.packed.bytes, en.n, en.k, en.group, pb);
@@ -221,33 +272,75 @@ static int parse_manifest(const char *text, Manifest *m) {
                          en.scales.count, en.n, en.k, en.group, sc);
         if (en.scales.bytes != en.scales.count * 2)
             return qfail(QM_SHAPE, "quant manifest: %s records %lld scale bytes for %lld bf16 scales", where, en.scales.bytes, en.scales.count);
-        if (find_entry(*m, en.layer, en.role.c_str()) >= 0) return qfail(QM_SHAPE, "quant manifest: %s appears twice", where);
         m->entries.push_back(en);
     }
+    return QM_OK;
+}
 
-    if (pairs->a.size() > (size_t)kMaxPairs) return qfail(QM_SHAPE, "quant manifest: more than %d pairs", kMaxPairs);
-    for (const Json &pj : pairs->a) {
-        if (pj.kind != Json::Obj) return qfail(QM_SYNTAX, "quant manifest: a pair is not an object");
+static int read_pairs(const Json &arr, Manifest *m) {
+    if (arr.kind != Json::Arr) return qfail(QM_SYNTAX, "quant manifest: pairs is not a list");
+    for (const Json &pj : arr.a) {
+        if (m->pairs.size() >= (size_t)kMaxPairs) return qfail(QM_FORMAT, "quant manifest: more than %d pairs", kMaxPairs);
+        if (pj.kind != Json::Obj || pj.o.empty()) return qfail(QM_SYNTAX, "quant manifest: a pair is not a filled object");
         Pair pr;
-        long long layer = -1;
-        const Json *members = pj.get("members");
-        if (!as_str(pj.get("name"), &pr.name) || !as_int(pj.get("layer"), &layer) || !as_int(pj.get("group"), &pr.group) ||
-            !read_shape(pj.get("logical_shape"), &pr.n, &pr.k) || !members || members->kind != Json::Arr || members->a.size() != 2)
-            return qfail(QM_SYNTAX, "quant manifest: a pair lacks name, layer, group, logical_shape or its two members");
-        pr.layer = (int)layer;
+        static const char *const kNames[7] = {"name", "layer", "logical_shape", "packed", "scales", "group", "members"};
+        bool seen[7] = {};
+        for (const auto &kv : pj.o) {
+            int st = need_key(kv.first);
+            if (st) return st;
+            int which = -1;
+            for (int i = 0; i < 7; ++i) if (kv.first == kNames[i]) which = i;
+            if (which < 0) { if ((st = skipped(kv.second, 0))) return st; continue; }
+            if (seen[which]) return qfail(QM_SYNTAX, "quant manifest: \"%s\" appears twice in a pair", kNames[which]);
+            seen[which] = true;
+            long long v = 0;
+            switch (which) {
+                case 0: st = need_str(kv.second, kNameMax, &pr.name, "a pair's name"); break;
+                case 1: st = need_int(kv.second, &v, "a pair's layer"); pr.layer = (int)v; break;
+                case 2: st = read_shape(kv.second, &pr.n, &pr.k); break;
+                case 3: st = read_artifact(kv.second, &pr.packed, false); break;
+                case 4: st = read_artifact(kv.second, &pr.scales, true); break;
+                case 5: st = need_int(kv.second, &pr.group, "a pair's group"); break;
+                default: {
+                    const Json &ms = kv.second;
+                    if (ms.kind != Json::Arr || ms.a.size() != 2) { st = qfail(QM_SYNTAX, "quant manifest: a pair's members are not a list of two"); break; }
+                    for (int i = 0; i < 2 && !st; ++i) {
+                        const Json &mj = ms.a[i];
+                        if (mj.kind != Json::Obj || mj.o.empty()) { st = qfail(QM_SYNTAX, "quant manifest: a pair member is not a filled object"); break; }
+                        bool seen_role = false, seen_index = false;
+                        for (const auto &mk : mj.o) {
+                            if ((st = need_key(mk.first))) break;
+                            if (mk.first == "role") {
+                                if (seen_role) { st = qfail(QM_SYNTAX, "quant manifest: a pair member names its role twice"); break; }
+                                seen_role = true;
+                                st = need_str(mk.second, kNameMax, &pr.member_role[i], "a pair member's role");
+                            } else if (mk.first == "role_index") {
+                                if (seen_index) { st = qfail(QM_SYNTAX, "quant manifest: a pair member gives its role_index twice"); break; }
+                                seen_index = true;
+                                long long ri = 0;
+                                st = need_int(mk.second, &ri, "a pair member's role_index");
+                                pr.member_role_index[i] = (int)ri;
+                            } else {
+                                st = skipped(mk.second, 0);
+                            }
+                            if (st) break;
+                        }
+                        if (!st && !seen_role) st = qfail(QM_SYNTAX, "quant manifest: a pair member has no role");
+                    }
+                }
+            }
+            if (st) return st;
+        }
+        for (bool b : seen) if (!b) return qfail(QM_SYNTAX, "quant manifest: a pair lacks one of name/layer/members/logical_shape/packed/scales/group");
+        if (pr.member_role[0].empty() || pr.member_role[1].empty()) return qfail(QM_SYNTAX, "quant manifest: a pair has fewer than two named members");
         char where[160];
         snprintf(where, sizeof(where), "pair %s layer %d", pr.name.c_str(), pr.layer);
-        int st;
-        if ((st = read_artifact(pj.get("packed"), &pr.packed, "u8", where, false))) return st;
-        if ((st = read_artifact(pj.get("scales"), &pr.scales, "bf16", where, true))) return st;
+        int st = check_artifact(pr.packed, "u8", where, false);
+        if (!st) st = check_artifact(pr.scales, "bf16", where, true);
+        if (st) return st;
         if (pr.n <= 0 || pr.k <= 0) return qfail(QM_SHAPE, "quant manifest: %s has a nonpositive shape", where);
         long long rows = 0, pbytes = 0, scales = 0, k = -1;
         for (int i = 0; i < 2; ++i) {
-            const Json &mj = members->a[i];
-            long long ri = -1;
-            if (mj.kind != Json::Obj || !as_str(mj.get("role"), &pr.member_role[i]))
-                return qfail(QM_SYNTAX, "quant manifest: %s has a member without a role", where);
-            if (as_int(mj.get("role_index"), &ri)) pr.member_role_index[i] = (int)ri;
             const int idx = find_entry(*m, pr.layer, pr.member_role[i].c_str());
             if (idx < 0)
                 return qfail(QM_SHAPE, "quant manifest: %s names member %s, which is not an entry of layer %d", where,
@@ -268,23 +361,36 @@ static int parse_manifest(const char *text, Manifest *m) {
         if (pr.group != FFN_INT4_GROUP) return qfail(QM_FORMAT, "quant manifest: %s groups %lld, the format groups %d", where, pr.group, FFN_INT4_GROUP);
         m->pairs.push_back(pr);
     }
+    return QM_OK;
+}
 
-    /* the precision map and the entries have to describe the same cells */
+/* the precision map and the entries have to describe the same cells */
+static int read_precision_map(const Json &arr, Manifest *m) {
+    if (arr.kind != Json::Arr) return qfail(QM_SYNTAX, "quant manifest: precision_map is not a list");
+    if (arr.a.empty()) return qfail(QM_FORMAT, "quant manifest: the precision map is empty");
     std::vector<char> seen(m->entries.size(), 0);
-    for (const Json &c : precision->a) {
+    for (const Json &c : arr.a) {
+        if (c.kind != Json::Obj || c.o.empty()) return qfail(QM_SYNTAX, "quant manifest: a precision cell is not a filled object");
         std::string role, prec;
         long long layer = -1;
-        if (c.kind != Json::Obj || !as_str(c.get("role"), &role) || !as_str(c.get("precision"), &prec) || !as_int(c.get("layer"), &layer))
-            return qfail(QM_SYNTAX, "quant manifest: a precision cell lacks role, layer or precision");
+        bool seen_role = false, seen_layer = false, seen_prec = false;
+        for (const auto &kv : c.o) {
+            int st = need_key(kv.first);
+            if (st) return st;
+            if (kv.first == "role") { seen_role = true; st = need_str(kv.second, kNameMax, &role, "a precision cell's role"); }
+            else if (kv.first == "layer") { seen_layer = true; st = need_int(kv.second, &layer, "a precision cell's layer"); }
+            else if (kv.first == "precision") { seen_prec = true; st = need_str(kv.second, kNameMax, &prec, "a precision cell's precision"); }
+            else st = skipped(kv.second, 0);
+            if (st) return st;
+        }
+        if (!seen_role || !seen_layer || !seen_prec) return qfail(QM_SYNTAX, "quant manifest: a precision cell lacks role, layer or precision");
         if (prec == "int4") {
             const int idx = find_entry(*m, (int)layer, role.c_str());
             if (idx < 0) return qfail(QM_SHAPE, "quant manifest: %s layer %lld is marked int4 but has no entry", role.c_str(), layer);
-            if (seen[idx]) return qfail(QM_SHAPE, "quant manifest: %s layer %lld has two precision cells", role.c_str(), layer);
+            if (seen[idx]) return qfail(QM_SHAPE, "quant manifest: %s layer %lld has two int4 precision cells", role.c_str(), layer);
             seen[idx] = 1;
             ++m->int4_cells;
         } else if (prec == "bf16") {
-            if (find_entry(*m, (int)layer, role.c_str()) >= 0)
-                return qfail(QM_SHAPE, "quant manifest: %s layer %lld has an entry but is marked bf16", role.c_str(), layer);
             ++m->bf16_cells;
         } else {
             return qfail(QM_FORMAT, "quant manifest: unknown precision %s", prec.c_str());
@@ -293,6 +399,74 @@ static int parse_manifest(const char *text, Manifest *m) {
     for (size_t i = 0; i < seen.size(); ++i)
         if (!seen[i])
             return qfail(QM_SHAPE, "quant manifest: %s layer %d has an entry but no int4 precision cell", m->entries[i].role.c_str(), m->entries[i].layer);
+    return QM_OK;
+}
+
+static int parse_manifest(const char *text, Manifest *m) {
+    if (!text || !m) return qfail(QM_ARG, "quant manifest: null argument");
+    JsonReader reader(text);
+    reader.manifest_dialect = true;
+    Json root;
+    reader.ws();
+    if (reader.p >= reader.end || *reader.p != '{') return qfail(QM_SYNTAX, "quant manifest: the document is not an object");
+    if (!reader.value(root)) return qfail(QM_SYNTAX, "%s", reader.error.c_str());
+    reader.ws();
+    if (reader.p != reader.end) return qfail(QM_SYNTAX, "quant manifest: bytes follow the document");
+    if (root.o.empty()) return qfail(QM_SYNTAX, "quant manifest: the document is empty");
+    bool seen_version = false, seen_format = false, seen_converter = false, seen_source = false, seen_entries = false,
+         seen_precision = false, seen_pairs = false;
+    long long version = 0;
+    for (const auto &kv : root.o) {
+        int st = need_key(kv.first);
+        if (st) return st;
+        bool *seen = kv.first == "manifest_version" ? &seen_version : kv.first == "format" ? &seen_format
+                   : kv.first == "converter" ? &seen_converter : kv.first == "source" ? &seen_source
+                   : kv.first == "entries" ? &seen_entries : kv.first == "precision_map" ? &seen_precision
+                   : kv.first == "pairs" ? &seen_pairs : nullptr;
+        if (!seen) { if ((st = skipped(kv.second, 0))) return st; continue; }
+        if (*seen) return qfail(QM_SYNTAX, "quant manifest: \"%s\" appears twice", kv.first.c_str());
+        *seen = true;
+        const Json &v = kv.second;
+        if (seen == &seen_version) {
+            st = need_int(v, &version, "manifest_version");
+        } else if (seen == &seen_format) {
+            st = read_format(v, m);
+        } else if (seen == &seen_converter || seen == &seen_source) {
+            const bool conv = seen == &seen_converter;
+            if (v.kind != Json::Obj || v.o.empty()) return qfail(QM_SYNTAX, "quant manifest: %s is not a filled object", conv ? "converter" : "source");
+            for (const auto &ck : v.o) {
+                if ((st = need_key(ck.first))) return st;
+                long long cv = 0;
+                if (conv && ck.first == "name") st = need_str(ck.second, kPathMax, &m->converter_name, "the converter's name");
+                else if (conv && ck.first == "version") { st = need_int(ck.second, &cv, "the converter's version"); m->converter_version = (int)cv; }
+                else if (!conv && ck.first == "model_dir") st = need_str(ck.second, kPathMax, &m->source_model_dir, "the source's model_dir");
+                else st = skipped(ck.second, 0);
+                if (st) return st;
+            }
+        } else if (seen == &seen_entries) {
+            st = read_entries(v, m);
+        } else if (seen == &seen_precision) {
+            if (!seen_entries) return qfail(QM_SYNTAX, "quant manifest: precision_map precedes entries, so it cannot be checked against them");
+            st = read_precision_map(v, m);
+        } else {
+            if (!seen_entries) return qfail(QM_SYNTAX, "quant manifest: pairs precede entries, so a pair cannot be checked against its members");
+            st = read_pairs(v, m);
+        }
+        if (st) return st;
+    }
+    if (!seen_version || !seen_format || !seen_converter || !seen_source || !seen_entries || !seen_precision)
+        return qfail(QM_SYNTAX, "quant manifest: one of manifest_version/format/converter/source/entries/precision_map is missing");
+    if (version != 1) return qfail(QM_FORMAT, "quant manifest: manifest_version %lld, this reader speaks 1", version);
+    m->manifest_version = 1;
+    if (m->converter_name.empty() || m->converter_version <= 0) return qfail(QM_FORMAT, "quant manifest: the converter is unnamed or unversioned");
+    if (m->source_model_dir.empty()) return qfail(QM_FORMAT, "quant manifest: no source model directory");
+    if (m->entries.empty()) return qfail(QM_FORMAT, "quant manifest: no entries");
+    /* one refusal of this reader's own, after everything the reference checks: an artifact path may not leave the sidecar */
+    auto outside = [](const Artifact &a) { return a.file[0] == '/' || a.file.find("..") != std::string::npos; };
+    for (const Entry &e : m->entries)
+        if (outside(e.packed) || outside(e.scales)) return qfail(QM_FORMAT, "quant manifest: %s layer %d names an artifact outside the sidecar directory", e.role.c_str(), e.layer);
+    for (const Pair &pr : m->pairs)
+        if (outside(pr.packed) || outside(pr.scales)) return qfail(QM_FORMAT, "quant manifest: pair %s layer %d names an artifact outside the sidecar directory", pr.name.c_str(), pr.layer);
     return QM_OK;
 }
 
