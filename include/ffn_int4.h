@@ -284,7 +284,8 @@ int ffn_quant_manifest_pair_shape(const FfnQuantManifest *manifest, int index, l
                                   long long *group);
 
 /* Replaces quant_artifact_read (quant_manifest.h:139-143; csrc/quant_manifest.c:1085-1139): reads
- * root/file, requiring the recorded size, then the expected dtype, then the SHA-256, in that order.
+ * root/file, requiring the expected dtype (want_dtype may be NULL: no expectation), then the recorded
+ * size, then the SHA-256, in that order.
  * On success *out is a malloc'd buffer the caller releases with ffn_host_free; on refusal *out is NULL. */
 int ffn_quant_artifact_read(const char *root, const char *file, const char *dtype, long long bytes,
                             const char *sha256, const char *want_dtype, uint8_t **out, size_t *out_len);
