@@ -470,7 +470,7 @@ static int parse_manifest(const char *text, Manifest *m) {
     return QM_OK;
 }
 
-/* Read one artifact, checking size, dtype and SHA-256 in that order (quant_artifact_read,
+/* Read one artifact, checking dtype, size and SHA-256 in that order (quant_artifact_read,
  * csrc/quant_manifest.c:1085-1139). */
 static int read_artifact_file(const std::string &root, const Artifact &a, const char *want_dtype, std::vector<uint8_t> *out) {
     if (want_dtype && a.dtype != want_dtype) /* a caller that passes no expectation gets no dtype check, as in the reference */
