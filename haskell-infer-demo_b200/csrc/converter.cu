@@ -460,44 +460,15 @@ extern "C" int ffn_convert_checkpoint(const char *model_dir, const char *descrip
     struct Written { int layer; std::string role; int role_index; long long n, k; std::vector<uint8_t> packed, scales; };
     std::vector<std::unique_ptr<Written>> gate_up; /* members kept until their layer's pair is written */
     std::vector<float> source;
-    for (const Instance &inst : instances) {
-        const auto found = index.find(inst.tensor);
-        if (found == index.end()) return fail(FFN_ERR_WEIGHTS, "ffn_convert_checkpoint: %s is not in the checkpoint", inst.tensor.c_str());
-        st = read_tensor_f32(inst.tensor, found->second, source);
-        if (st) return st;
-        const long long n = found->second.shape[0], k = found->second.shape[1];
-        std::unique_ptr<Written> w(new Written{inst.layer, inst.role, inst.role_index, n, k, {}, {}});
-        st = quantize_tensor(dev, source, n, k, w->packed, w->scales, err);
-        if (st) return st;
-        const std::string stem = inst.role + "_layer" + std::to_string(inst.layer);
-        if (!write_whole_file(art_dir + "/" + stem + ".packed", w->packed.data(), w->packed.size()) ||
-            !write_whole_file(art_dir + "/" + stem + ".scales", w->scales.data(), w->scales.size()))
-            return fail(FFN_ERR_WEIGHTS, "ffn_convert_checkpoint: cannot write the artifacts of %s", stem.c_str());
-        JOut e = JOut::obj();
-        e["role"] = JOut::str(inst.role);
-        e["role_index"] = JOut::integer(inst.role_index);
-        e["layer"] = JOut::integer(inst.layer);
-        e["checkpoint_tensor"] = JOut::str(inst.tensor);
-        JOut shape = JOut::arr();
-        shape.a.push_back(JOut::integer(n)); shape.a.push_back(JOut::integer(k));
-        e["logical_shape"] = shape;
-        e["local_shape"] = shape;
-        e["packed"] = artifact_json("artifacts/" + stem + ".packed", "u8", w->packed, false);
-        e["scales"] = artifact_json("artifacts/" + stem + ".scales", "bf16", w->scales, true);
-        e["group_axis"] = JOut::str("k");
-        e["group"] = JOut::integer(FFN_INT4_GROUP);
-        entries.a.push_back(e);
-        if (inst.role == "mlpGate" || inst.role == "mlpUp") gate_up.push_back(std::move(w));
-    }
-
-    /* ---- the gate||up pair of every layer that has both members: byte concatenation, gate rows first */
-    for (int layer = 0; layer < num_layers; ++layer) {
+    /* ---- the gate||up pair of a layer, as soon as both members exist (their bytes are dropped right after):
+     * byte concatenation, gate rows first */
+    auto emit_pair = [&](int layer) -> int {
         const Written *gate = nullptr, *up = nullptr;
         for (const auto &w : gate_up) {
             if (w->layer != layer) continue;
             if (w->role == "mlpGate") gate = w.get(); else up = w.get();
         }
-        if (!gate || !up) continue;
+        if (!gate || !up) return FFN_OK;
         if (gate->k != up->k) return fail(FFN_ERR_WEIGHTS, "ffn_convert_checkpoint: layer %d's gate and up differ in K", layer);
         std::vector<uint8_t> packed(gate->packed), scales(gate->scales);
         packed.insert(packed.end(), up->packed.begin(), up->packed.end());
@@ -526,6 +497,42 @@ extern "C" int ffn_convert_checkpoint(const char *model_dir, const char *descrip
         p["scales"] = artifact_json("artifacts/" + stem + ".scales", "bf16", scales, true);
         p["group"] = JOut::integer(FFN_INT4_GROUP);
         pairs.a.push_back(p);
+        gate_up.erase(std::remove_if(gate_up.begin(), gate_up.end(), [&](const std::unique_ptr<Written> &w) { return w->layer == layer; }),
+                      gate_up.end());
+        return FFN_OK;
+    };
+
+    for (const Instance &inst : instances) {
+        const auto found = index.find(inst.tensor);
+        if (found == index.end()) return fail(FFN_ERR_WEIGHTS, "ffn_convert_checkpoint: %s is not in the checkpoint", inst.tensor.c_str());
+        st = read_tensor_f32(inst.tensor, found->second, source);
+        if (st) return st;
+        const long long n = found->second.shape[0], k = found->second.shape[1];
+        std::unique_ptr<Written> w(new Written{inst.layer, inst.role, inst.role_index, n, k, {}, {}});
+        st = quantize_tensor(dev, source, n, k, w->packed, w->scales, err);
+        if (st) return st;
+        const std::string stem = inst.role + "_layer" + std::to_string(inst.layer);
+        if (!write_whole_file(art_dir + "/" + stem + ".packed", w->packed.data(), w->packed.size()) ||
+            !write_whole_file(art_dir + "/" + stem + ".scales", w->scales.data(), w->scales.size()))
+            return fail(FFN_ERR_WEIGHTS, "ffn_convert_checkpoint: cannot write the artifacts of %s", stem.c_str());
+        JOut e = JOut::obj();
+        e["role"] = JOut::str(inst.role);
+        e["role_index"] = JOut::integer(inst.role_index);
+        e["layer"] = JOut::integer(inst.layer);
+        e["checkpoint_tensor"] = JOut::str(inst.tensor);
+        JOut shape = JOut::arr();
+        shape.a.push_back(JOut::integer(n)); shape.a.push_back(JOut::integer(k));
+        e["logical_shape"] = shape;
+        e["local_shape"] = shape;
+        e["packed"] = artifact_json("artifacts/" + stem + ".packed", "u8", w->packed, false);
+        e["scales"] = artifact_json("artifacts/" + stem + ".scales", "bf16", w->scales, true);
+        e["group_axis"] = JOut::str("k");
+        e["group"] = JOut::integer(FFN_INT4_GROUP);
+        entries.a.push_back(e);
+        if (inst.role == "mlpGate" || inst.role == "mlpUp") {
+            gate_up.push_back(std::move(w));
+            if ((st = emit_pair(inst.layer))) return st;
+        }
     }
 
     /* ---- the precision map: every role of every layer, quantized or retained */
