@@ -15,6 +15,8 @@
 
 namespace ffn {
 
+#define FFN_INT4_STR2(x) #x
+#define FFN_INT4_STR(x) FFN_INT4_STR2(x)
 static thread_local char g_error[512];
 static int g_fused_enabled = 1;
 
@@ -152,6 +154,16 @@ int ffn_int4_describe_plan(int tokens, int hidden, int intermediate, int sm_coun
     return FFN_OK;
 }
 
+int ffn_int4_describe_gemm_plan(int m, int n, int k, int sm_count, int smem_optin, char *out, size_t out_bytes) {
+    clear_error();
+    if (!out || out_bytes < 64) return fail(FFN_ERR_CONFIG, "ffn_int4_describe_gemm_plan: the text buffer is too small");
+    if (m < 1 || n <= 0 || k <= 0 || k % FFN_INT4_GROUP || sm_count < 1 || smem_optin < 1)
+        return fail(FFN_ERR_CONFIG, "ffn_int4_describe_gemm_plan: invalid shape or device description");
+    if (m <= 2 && gemv_describe_plan(m, n, k, sm_count, smem_optin, out, out_bytes)) return FFN_OK;
+    snprintf(out, out_bytes, "kernel=generic launches=1");
+    return FFN_OK;
+}
+
 int ffn_int4_set_fused(int enabled) {
     const int old = g_fused_enabled;
     g_fused_enabled = enabled != 0;
@@ -160,25 +172,55 @@ int ffn_int4_set_fused(int enabled) {
 
 void ffn_int4_debug_trace(void *device_buffer) { fused_set_trace((long long *)device_buffer); }
 
-int ffn_int4_device_status(int *where, int *cta) {
-    clear_error();
-    unsigned st = 0;
-    const cudaError_t e = cudaDeviceSynchronize();
-    if (e != cudaSuccess) return fail(FFN_ERR_CUDA, "ffn_int4_device_status: %s", cudaGetErrorString(e));
-    const int rc = fused_status(&st, true);
-    if (rc) return rc;
+static int report_status(unsigned st, int *where, int *cta) {
     if (where) *where = (int)(st & 0xFF);
     if (cta) *cta = (int)(st >> 8);
     if (st != 0) {
         static const char *names[] = {"", "producer waiting for a free stage", "consumer waiting for weights",
                                       "consumer waiting for a partial slot", "epilogue waiting for partials",
                                       "grid barrier", "a peer rank's partial sums", "draining copies",
-                                      "consumer waiting for the activation vector"};
+                                      "consumer waiting for the activation vector", "waiting for the other CTAs' partial sums",
+                                      "waiting for the residual stream of the next layer", "waiting for this CTA's own activations"};
         const unsigned w = st & 0xFF;
         return fail(FFN_ERR_CUDA, "a bounded device-side wait ran out (%s, CTA %u); the kernel returned early and "
-                    "its output is invalid", w < 9 ? names[w] : "unknown", st >> 8);
+                    "its output is invalid", w < sizeof(names) / sizeof(names[0]) ? names[w] : "unknown", st >> 8);
     }
     return FFN_OK;
+}
+
+int ffn_int4_device_status(int *where, int *cta) {
+    clear_error();
+    unsigned st = 0;
+    const cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(FFN_ERR_CUDA, "ffn_int4_device_status: %s", cudaGetErrorString(e));
+    int rc = fused_status(&st, true);
+    if (rc) return rc;
+    if (st == 0 && fused_noalloc_in_use()) { /* the allocation-free entry point keeps its own status word */
+        rc = fused_status_noalloc(&st, true);
+        if (rc) return rc;
+    }
+    return report_status(st, where, cta);
+}
+
+int ffn_int4_noalloc_status(int *where, int *cta) {
+    clear_error();
+    unsigned st = 0;
+    const cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(FFN_ERR_CUDA, "ffn_int4_noalloc_status: %s", cudaGetErrorString(e));
+    const int rc = fused_status_noalloc(&st, true);
+    if (rc) return rc;
+    return report_status(st, where, cta);
+}
+
+unsigned ffn_tp_exchange_tag(unsigned call_number) { return tp_tag(call_number); }
+
+const char *ffn_int4_numerical_policy(void) {
+    /* Sorted keys, no whitespace: ready to be spliced into the fields of a numerical_policy block. */
+    return "\"ffn_int4_accumulate\":\"block_fixed_point_a16_dp4a_per_32_fp32_across;mma_bf16_codes_fp32_per_group\","
+           "\"ffn_int4_kernel\":\"b200_ffn_int4_abi" FFN_INT4_STR(FFN_INT4_ABI_VERSION) "\","
+           "\"ffn_int4_roundings\":\"gate_up_bf16;silu_mul_bf16;down_bf16_after_reduce\","
+           "\"ffn_tp_reduce\":\"fp32_partials_rank_order_single_rounding\","
+           "\"weight_quantization\":\"int4_symmetric_group_bf16_scale_decode_only\"";
 }
 
 int ffn_gemm_int4_bf16(const void *a, const void *packed, const void *scales, void *out, int M, int N,

@@ -93,8 +93,17 @@ struct FusedParams {
     float norm_eps;
     int norm_gemma;
     long long *trace;     /* optional [kTraceWords] clock64 stamps of CTA 0 (NULL = off) */
-    int debug;            /* measurement aid: bit 0 skips the arithmetic, bit 1 skips the weight copies */
+    int gemv;             /* 1: single-matrix mode - only phase 2 runs, its activation is the caller's input
+                             (no grid barrier, nothing handed over between phases) */
+#ifdef FFN_INT4_TUNING
+    int debug;            /* measurement build only: bit 0 skips the arithmetic, bit 1 skips the weight copies */
+#endif
 };
+#ifdef FFN_INT4_TUNING
+#define FFN_DEBUG_BIT(P, b) ((P).debug & (b))
+#else
+#define FFN_DEBUG_BIT(P, b) 0
+#endif
 
 /* ---- PTX wrappers -------------------------------------------------------------------------- */
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -225,10 +234,14 @@ __device__ __forceinline__ void prepare_chunk(XChunk &xc, uint32_t (&v)[16], boo
     for (int i = 0; i < 16; ++i) mx = __vmaxu2(mx, v[i] & 0x7FFF7FFFu);
     const uint32_t top = max(mx & 0xFFFFu, mx >> 16);
     const int E = (int)(top >> 7); /* biased exponent of the largest magnitude */
-    /* E < 19 (|x| < 2^-108) is treated as an all-zero slice; Inf/NaN inputs are outside the contract */
+    /* E < 19 (|x| < 2^-108) is treated as an all-zero slice.  A slice that holds an Inf or a NaN
+     * (E == 255) gets fac = NaN, so every row's sum becomes NaN: non-finite inputs give non-finite
+     * outputs, as the reference's FMA chain does (csrc/kernels/gemm_quant.cu:182-199), at no cost
+     * in the inner loop. */
     const bool live = E >= 19 && E < 255;
     const float up = live ? __uint_as_float((uint32_t)(268 - E) << 23) : 0.0f;   /* 2^(141-E) */
-    xc.fac = live ? __uint_as_float((uint32_t)(E - 18) << 23) : 0.0f;            /* 2^(E-141) / 16 */
+    xc.fac = live ? __uint_as_float((uint32_t)(E - 18) << 23)                    /* 2^(E-141) / 16 */
+                  : (E == 255 ? __uint_as_float(0x7FC00000u) : 0.0f);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         int X[8];
@@ -444,7 +457,7 @@ __device__ __forceinline__ void consume_phase(const FusedParams &P, const PhaseP
         float val[VALS];
 #pragma unroll
         for (int v = 0; v < VALS; ++v) val[v] = 0.0f;
-        if (active && !(P.debug & 1)) {
+        if (active && !FFN_DEBUG_BIT(P, 1)) {
             /* No data-dependent branches in here: a column chunk past the row end reads a clamped
              * address against an all-zero prepared slice, a row past the tile end reads the tile's
              * last row and its value is dropped at the store.  That leaves the compiler free to
@@ -544,7 +557,7 @@ __device__ __forceinline__ bool epilogue_phase(const FusedParams &P, const Phase
                         f32_to_bf16_bits(bf16_bits_to_f32(P.residual[(size_t)m * P.H + row]) + y);
             } else {
                 const size_t off = (size_t)((seq & 1u) * P.tp + P.rank) * P.slot_stride + (size_t)m * P.H + row;
-                for (int r = 0; r < P.tp; ++r) tp_store_tagged(P.peer_slots[r] + off, a, seq + 1u); /* own slot on every rank */
+                for (int r = 0; r < P.tp; ++r) tp_store_tagged(P.peer_slots[r] + off, a, tp_tag(seq)); /* own slot on every rank */
             }
         }
         __syncwarp();
@@ -592,7 +605,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
             /* Phase 2's activation vector is fetched once the grid barrier has opened (every CTA has
              * stored its rows of act). */
             auto fetch_act = [&]() {
-                bool open = false;
+                bool open = P.gemv != 0; /* single-matrix mode: the activation is an input, present from the start */
                 for (uint32_t i = 0; i < kSpinLimit && !open; ++i) {
                     open = (int)(ld_acquire_gpu(P.sync + 0) - bar_target) >= 0;
                     if (!open) {
@@ -606,6 +619,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
                 bulk_g2s(xs, P.act, (uint32_t)(P.M * P.I * 2), &sm->x_full[1]);
                 act_issued = true;
             };
+            if (P.gemv) fetch_act();
             for (; t < total && !failed; ++t) {
                 const int s = t % ns;
                 /* A stage that still holds a phase-2 tile is only released after the consumers got
@@ -618,7 +632,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
                     break;
                 }
                 uint8_t *dst = ring + (size_t)s * P.stage_bytes;
-                if (P.debug & 2) { mbar_arrive(&sm->full[s]); continue; }
+                if (FFN_DEBUG_BIT(P, 2)) { mbar_arrive(&sm->full[s]); continue; }
                 if (t < nt1) {
                     const int r0 = b1 + t * P.p1.TR, rows = min(P.p1.TR, e1 - r0);
                     const uint32_t bytes = (uint32_t)rows * P.p1.rb;
@@ -661,19 +675,22 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
         }
     } else if (warp <= kConsumerWarps) {
         /* ---------------- consumers ---------------- */
-        consume_phase<CIT1, MT, true>(P, P.p1, sm, xs, ring, 0);
+        if (!P.gemv) consume_phase<CIT1, MT, true>(P, P.p1, sm, xs, ring, 0);
         if (!sm->abort_flag) consume_phase<CIT2, MT, false>(P, P.p2, sm, xs, ring, nt1);
     } else {
         /* ---------------- epilogue ---------------- */
         /* read before this CTA arrives at the grid barrier: nobody can have advanced it yet */
         const unsigned seq = P.tp > 1 ? ld_acquire_gpu(P.tp_seq) : 0u;
-        bool ok = epilogue_phase<MT, true>(P, P.p1, sm, 0, seq);
-        /* arrive at the grid barrier: the act rows of this CTA are stored */
-        __threadfence(); /* every lane publishes its own act stores */
-        __syncwarp();
-        if (lane == 0) {
-            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.sync + 0) : "memory");
-            stamp(P, 5);
+        bool ok = true;
+        if (!P.gemv) {
+            ok = epilogue_phase<MT, true>(P, P.p1, sm, 0, seq);
+            /* arrive at the grid barrier: the act rows of this CTA are stored */
+            __threadfence(); /* every lane publishes its own act stores */
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.sync + 0) : "memory");
+                stamp(P, 5);
+            }
         }
         if (ok) ok = epilogue_phase<MT, false>(P, P.p2, sm, nt1, seq);
         if (lane == 0) stamp(P, 10);
@@ -689,11 +706,11 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
                     for (int r = 0; r < P.tp && all_in; ++r) {
                         const unsigned long long *p = mine + (size_t)r * P.slot_stride + (size_t)m * P.H + row;
                         float v = 0.0f;
-                        bool in = tp_load_tagged(p, seq + 1u, &v);
+                        bool in = tp_load_tagged(p, tp_tag(seq), &v);
                         for (uint32_t k = 0; !in && k < kTpPollLimit; ++k) {
                             if ((k & 1023u) == 1023u && sm->abort_flag) break; /* another lane already gave up */
                             __nanosleep(20);
-                            in = tp_load_tagged(p, seq + 1u, &v);
+                            in = tp_load_tagged(p, tp_tag(seq), &v);
                         }
                         all_in = in;
                         a += v;
@@ -712,7 +729,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
     __syncthreads();
     /* the call sequence number advances once per launch (parity of the peer slots, tag of the exchanged words) */
     if (blockIdx.x == 0 && threadIdx.x == 0) {
-        P.sync[1] += gridDim.x; /* every CTA has arrived by now (this CTA passed the barrier) */
+        if (!P.gemv) P.sync[1] += gridDim.x; /* every CTA has arrived by now (this CTA passed the barrier) */
         if (P.tp > 1) atomicAdd(P.tp_seq, 1u);
         stamp(P, 12);
     }
@@ -819,11 +836,14 @@ constexpr int kDefaultStageTarget = 62 * 1024; /* bytes of weights per stage the
 
 template <int C1, int C2, int MT>
 static int launch_fused(DeviceState &d, const FusedParams &P, int grid, size_t smem, cudaStream_t stream) {
-    bool &set = d.attr_set[C1 - 1][C2 - 1][MT - 1];
-    if (!set) {
-        FFN_CUDA_TRY(cudaFuncSetAttribute(ffn_fused_kernel<C1, C2, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          d.smem_optin), "fused FFN: shared-memory opt-in");
-        set = true;
+    {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        bool &set = d.attr_set[C1 - 1][C2 - 1][MT - 1];
+        if (!set) {
+            FFN_CUDA_TRY(cudaFuncSetAttribute(ffn_fused_kernel<C1, C2, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              d.smem_optin), "fused FFN: shared-memory opt-in");
+            set = true;
+        }
     }
     void *args[] = {(void *)&P};
     FFN_CUDA_TRY(cudaLaunchCooperativeKernel((const void *)ffn_fused_kernel<C1, C2, MT>, dim3(grid), dim3(kThreads),
@@ -862,15 +882,21 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
         P.tp_seq = tp->seq;
         if (tokens * H > tp->slot_stride) return fail(FFN_ERR_CONFIG, "fused FFN: %d tokens exceed the exchange buffer", tokens);
     }
-    static const int target_kb = getenv("FFN_INT4_STAGE_KB") ? atoi(getenv("FFN_INT4_STAGE_KB")) : kDefaultStageTarget / 1024; /* tuning knob */
+#ifdef FFN_INT4_TUNING
+    static const int target_kb = getenv("FFN_INT4_STAGE_KB") ? atoi(getenv("FFN_INT4_STAGE_KB")) : kDefaultStageTarget / 1024;
+#else
+    const int target_kb = kDefaultStageTarget / 1024;
+#endif
     int c1 = 0, c2 = 0;
     size_t smem = 0;
     if (!plan_fused(P, tokens, H, I, d.smem_optin, target_kb * 1024, c1, c2, smem)) return FFN_NOT_ADMITTED;
     P.p1.w = w->gate_up_i4; P.p1.s = (const uint16_t *)w->gate_up_i4_scales;
     P.p2.w = w->down_i4; P.p2.s = (const uint16_t *)w->down_i4_scales;
     P.trace = g_trace;
+#ifdef FFN_INT4_TUNING
     static const int debug_flags = getenv("FFN_INT4_DEBUG") ? atoi(getenv("FFN_INT4_DEBUG")) : 0;
     P.debug = debug_flags;
+#endif
     const int grid = d.sm_count; /* under TP every rank runs the same grid: CTA c owns the same rows everywhere */
 
 #define FFN_LAUNCH(A, B, C) return launch_fused<A, B, C>(d, P, grid, smem, stream)
@@ -966,9 +992,10 @@ int fused_ffn_launch_noalloc(cudaStream_t stream, const void *normed, void *laye
     P.p1.w = w->gate_up_i4; P.p1.s = (const uint16_t *)w->gate_up_i4_scales;
     P.p2.w = w->down_i4; P.p2.s = (const uint16_t *)w->down_i4_scales;
     /* The array keeps whatever the previous call left.  The barrier words must be consistent with
-     * each other and the status word must start at zero, so they are cleared on the stream first;
-     * act needs no clearing (phase 1 writes every element phase 2 reads). */
-    FFN_CUDA_TRY(cudaMemsetAsync(d.sync, 0, 4 * sizeof(unsigned), stream), "clear the static synchronisation words");
+     * each other, so they are cleared on the stream first; act needs no clearing (phase 1 writes
+     * every element phase 2 reads).  The status word (word 3) is NOT cleared here: a wait that ran
+     * out in an earlier call stays on record until ffn_int4_noalloc_status reads it. */
+    FFN_CUDA_TRY(cudaMemsetAsync(d.sync, 0, 3 * sizeof(unsigned), stream), "clear the static synchronisation words");
     const int grid = d.sm_count;
     if (tokens == 1) {
         if (c1 == 1 && c2 == 1) return launch_fused<1, 1, 1>(d, P, grid, smem, stream);
@@ -1003,6 +1030,30 @@ int fused_status_word(unsigned **out) {
     return FFN_OK;
 }
 
+/* The status word of the static-scratch entry point on the current device (no allocation: the
+ * array's address is looked up, the four words are copied to the host).  A device that never ran
+ * that entry point and has not resolved the array yet is resolved here. */
+int fused_status_noalloc(unsigned *status_out, bool reset) {
+    DeviceState *dp = nullptr;
+    unsigned char *scratch = nullptr;
+    const int st = noalloc_device_state(&dp, &scratch);
+    if (st) return st;
+    unsigned words[4];
+    FFN_CUDA_TRY(cudaMemcpy(words, dp->sync, sizeof(words), cudaMemcpyDeviceToHost), "read the static status word");
+    *status_out = words[3];
+    if (reset && words[3] != 0) FFN_CUDA_TRY(cudaMemset(dp->sync, 0, sizeof(words)), "reset the static synchronisation words");
+    return FFN_OK;
+}
+
+/* True once the static array has been resolved on the current device (i.e. the allocation-free
+ * entry point or its status reader ran there). */
+bool fused_noalloc_in_use() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    return g_noalloc_dev[dev].ready;
+}
+
 int fused_status(unsigned *status_out, bool reset) {
     DeviceState *dp = nullptr;
     const int st = device_state(&dp);
@@ -1014,8 +1065,80 @@ int fused_status(unsigned *status_out, bool reset) {
     return FFN_OK;
 }
 
+/* Geometry of a single-matrix launch (out[M][N] = a[M][K] x W[N][K]^T): the kernel's second phase
+ * alone, its activation vector being the caller's input.  Returns false when the kernel does not
+ * take the shape. */
+static bool plan_gemv(FusedParams &P, int tokens, int N, int K, int smem_optin, int target_bytes, int &c2, size_t &smem) {
+    if (tokens < 1 || tokens > 2) return false;
+    if (N <= 0 || K <= 0 || K % FFN_INT4_GROUP || N % 8) return false; /* N % 8: the scale array ends on a 16-byte boundary */
+    if (N > (1 << 22) || K > (1 << 22)) return false;
+    P.M = tokens; P.H = N; P.I = K;
+    P.gemv = 1;
+    P.p1 = PhasePlan();
+    P.p1.TR = 1; /* no rows: zero tiles */
+    if (!plan_phase(P.p2, K, tokens, false, target_bytes, c2)) return false;
+    P.p2.rows_total = N; P.p2.up_offset = 0;
+    const int part_floats = tokens == 1 ? kPartFloats1 : kPartFloats2;
+    if (P.p2.TR * tokens * P.p2.nhw > part_floats) return false;
+    P.stage_w_bytes = round_up(P.p2.TR * P.p2.rb, 128);
+    P.sc_half_bytes = round_up(P.p2.TR * P.p2.G * 2 + 32, 16);
+    P.stage_bytes = round_up(P.stage_w_bytes + P.sc_half_bytes, 128);
+    P.xs_bytes = round_up(tokens * K * 2, 128);
+    const size_t fixed = fused_smem_header(tokens) + (size_t)P.xs_bytes;
+    if (fixed + 2 * (size_t)P.stage_bytes > (size_t)smem_optin) return false;
+    P.nstages = (int)min((size_t)kMaxStages, ((size_t)smem_optin - fixed) / (size_t)P.stage_bytes);
+    smem = fixed + (size_t)P.nstages * P.stage_bytes;
+    return true;
+}
+
+/* One or two activation rows against one packed matrix through the streaming kernel (persistent
+ * CTA per SM, bulk-copy ring, dp4a inner product): the replacement for gemv_int4_kernel
+ * (csrc/kernels/gemm_quant.cu:165-200) on its own, i.e. for projections and the LM head as well as
+ * for the FFN's two matrices.  FFN_NOT_ADMITTED when the shape or the alignment is outside what the
+ * kernel takes. */
+static int gemv_int4_stream(const void *a, const void *packed, const void *scales, void *out, int M, int N, int K,
+                            cudaStream_t stream) {
+    if (M < 1 || M > 2) return FFN_NOT_ADMITTED;
+    if (((uintptr_t)a & 15) || ((uintptr_t)packed & 15) || ((uintptr_t)scales & 15)) return FFN_NOT_ADMITTED;
+    DeviceState *dp = nullptr;
+    const int st = device_state(&dp);
+    if (st) return st;
+    DeviceState &d = *dp;
+    if (!d.cooperative) return FFN_NOT_ADMITTED;
+    FusedParams P = {};
+    int c2 = 0;
+    size_t smem = 0;
+    if (!plan_gemv(P, M, N, K, d.smem_optin, kDefaultStageTarget, c2, smem)) return FFN_NOT_ADMITTED;
+    P.x = (const uint16_t *)a;
+    P.act = (uint16_t *)const_cast<void *>(a); /* read only: the producer copies it into shared memory */
+    P.out = (uint16_t *)out;
+    P.sync = d.sync;
+    P.tp = 1; P.rank = 0;
+    P.p2.w = (const uint8_t *)packed; P.p2.s = (const uint16_t *)scales;
+    P.trace = nullptr;
+    const int grid = min(d.sm_count, (N + P.p2.TR - 1) / P.p2.TR); /* no CTA without a tile */
+    if (M == 2) return launch_fused<1, 1, 2>(d, P, grid, smem, stream);
+    if (c2 == 1) return launch_fused<1, 1, 1>(d, P, grid, smem, stream);
+    return launch_fused<1, 2, 1>(d, P, grid, smem, stream);
+}
+
+bool gemv_describe_plan(int tokens, int N, int K, int sm_count, int smem_optin, char *out, size_t out_bytes) {
+    FusedParams P = {};
+    int c2 = 0;
+    size_t smem = 0;
+    if (!plan_gemv(P, tokens, N, K, smem_optin, kDefaultStageTarget, c2, smem)) return false;
+    snprintf(out, out_bytes, "kernel=stream_gemv grid=%d threads=%d smem=%zu stages=%d stage_bytes=%d x_bytes=%d cit=%d ct=%d rg=%d jt=%d rows_per_tile=%d",
+             min(sm_count, (N + P.p2.TR - 1) / P.p2.TR), kThreads, smem, P.nstages, P.stage_bytes, P.xs_bytes, c2, P.p2.CT, P.p2.RG,
+             P.p2.JT, P.p2.TR);
+    return true;
+}
+
 int gemm_int4_dispatch(const void *a, const void *packed, const void *scales, void *out, int M, int N,
                        int K, cudaStream_t stream) {
+    if (M <= 2) {
+        const int st = gemv_int4_stream(a, packed, scales, out, M, N, K, stream);
+        if (st != FFN_NOT_ADMITTED) return st;
+    }
     return gemm_int4_generic(a, packed, scales, out, nullptr, M, N, K, stream);
 }
 

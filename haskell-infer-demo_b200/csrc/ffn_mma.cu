@@ -29,6 +29,8 @@
  */
 #include <stdio.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -284,7 +286,7 @@ __global__ void __launch_bounds__(kMmaThreads) down_mma_kernel(const MmaParams P
         const float y = red[(size_t)r * ldr + m];
         const size_t o = (size_t)m * P.N + row0 + r;
         if (P.tp > 1) {
-            for (int q = 0; q < P.tp; ++q) tp_store_tagged(P.peer_slots[q] + slot + o, y, seq + 1u);
+            for (int q = 0; q < P.tp; ++q) tp_store_tagged(P.peer_slots[q] + slot + o, y, tp_tag(seq));
         } else {
             const float v = round_bf16(y);
             P.out[o] = f32_to_bf16_bits(v);
@@ -304,10 +306,10 @@ __global__ void __launch_bounds__(kMmaThreads) down_mma_kernel(const MmaParams P
             for (int q = 0; q < P.tp && all_in; ++q) {
                 const unsigned long long *p = mine + (size_t)q * P.slot_stride + o;
                 float v = 0.0f;
-                bool in = tp_load_tagged(p, seq + 1u, &v);
+                bool in = tp_load_tagged(p, tp_tag(seq), &v);
                 for (uint32_t k = 0; !in && k < kTpPollLimit; ++k) {
                     __nanosleep(40);
-                    in = tp_load_tagged(p, seq + 1u, &v);
+                    in = tp_load_tagged(p, tp_tag(seq), &v);
                 }
                 all_in = in;
                 y += v;
@@ -348,6 +350,7 @@ struct MmaScratch {
     size_t bytes = 0;
 };
 static MmaScratch g_mma_scratch[64];
+static std::mutex g_mma_mutex; /* guards the table above; the scratch itself is shared by every call on the device */
 
 /* Launch geometry of the pair for `nt` 8-token tiles: pipeline depth, shared memory per CTA, CTAs per
  * SM, and the K splits of the down projection (chosen to fill the device's CTA slots as evenly as
@@ -422,6 +425,7 @@ int mma_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *lay
     if ((size_t)(H / kMmaRows) * sizeof(unsigned) > counters) return FFN_NOT_ADMITTED;
     const size_t perm_bytes = ((size_t)64 * (H + I) * sizeof(uint16_t) + 255) / 256 * 256;
     const size_t want = counters + perm_bytes + (size_t)kMmaMaxSplits * 64 * H * sizeof(float);
+    std::lock_guard<std::mutex> lock(g_mma_mutex);
     MmaScratch &sc = g_mma_scratch[dev];
     if (sc.bytes < want) {
         if (sc.base) { FFN_CUDA_TRY(cudaDeviceSynchronize(), "batched INT4 FFN: scratch regrow"); cudaFree(sc.base); }

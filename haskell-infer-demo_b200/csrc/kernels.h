@@ -25,7 +25,8 @@ int dequantize_int4(void *out, const void *packed, const void *scales, int N, in
 
 /* ffn_fused.cu */
 #define FFN_NOT_ADMITTED 1 /* internal: the fused kernel does not take this shape */
-/* M-dispatching GEMM: decode-shaped calls go to the streaming kernels, the rest to the generic one. */
+/* M-dispatching GEMM: one or two activation rows go through the streaming kernel's single-matrix
+ * mode (when the shape and the alignment allow), everything else through the generic kernel. */
 int gemm_int4_dispatch(const void *a, const void *packed, const void *scales, void *out, int M, int N,
                        int K, cudaStream_t stream);
 /* The single-launch fused FFN (gate/up + SiLU*up + down).  Returns FFN_NOT_ADMITTED when the shape
@@ -46,6 +47,10 @@ constexpr int kTpMaxRanks = 16;
 constexpr size_t kTpSeqOffset = 0;
 constexpr size_t kTpHeaderBytes = 256;
 constexpr uint32_t kTpPollLimit = 1u << 20; /* polls of one tagged word before a receiver gives up (about a second) */
+
+/* The tag the exchange words of call number `seq` carry.  Never zero (zero marks a word nobody has
+ * written since the buffer was cleared), also when the 32-bit call counter wraps. */
+__host__ __device__ __forceinline__ unsigned tp_tag(unsigned seq) { return seq % 0xFFFFFFFFu + 1u; }
 
 __device__ __forceinline__ void tp_store_tagged(unsigned long long *p, float v, unsigned tag) {
     const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
@@ -79,6 +84,10 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
  * 0 = fine, else (where | cta << 8).  With reset, a non-zero status also clears the kernel's
  * synchronisation words so the next launch starts clean. */
 int fused_status(unsigned *status_out, bool reset);
+/* The same for the status word inside the static scratch array of the allocation-free entry point. */
+int fused_status_noalloc(unsigned *status_out, bool reset);
+bool fused_noalloc_in_use();
+bool gemv_describe_plan(int tokens, int N, int K, int sm_count, int smem_optin, char *out, size_t out_bytes);
 void fused_set_trace(long long *device_buffer);
 /* ffn_mma.cu: the tensor-core path for 3..64 tokens (two launches: gate/up + SiLU*up, down + reduce). */
 int mma_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,

@@ -43,6 +43,77 @@ static int tp_publish_tables(TpComm *c) {
     return FFN_OK;
 }
 
+/* Stand-alone all-reduce over the communicator's exchange slots: every thread pushes its elements
+ * (as FP32) into slot `rank` of every rank's buffer, then waits (bounded) for the tp words of each
+ * of its elements in its own buffer, adds them in rank order and stores the rounded sum in place. */
+template <typename T> struct ElemIo;
+template <> struct ElemIo<float> {
+    static __device__ __forceinline__ float load(const float *p) { return *p; }
+    static __device__ __forceinline__ void store(float *p, float v) { *p = v; }
+};
+template <> struct ElemIo<uint16_t> { /* bf16 bits */
+    static __device__ __forceinline__ float load(const uint16_t *p) { return bf16_bits_to_f32(*p); }
+    static __device__ __forceinline__ void store(uint16_t *p, float v) { *p = f32_to_bf16_bits(v); }
+};
+
+template <typename T>
+__global__ void tp_allreduce_kernel(T *buf, size_t elements, unsigned long long *const *peer_slots, int slot_stride,
+                                    int tp, int rank, const unsigned *seq_word, unsigned *status) {
+    const unsigned seq = *seq_word; /* advanced by the launch that follows this one on the stream */
+    const unsigned tag = tp_tag(seq);
+    const size_t par = (size_t)(seq & 1u) * tp * slot_stride;
+    const size_t stride = (size_t)gridDim.x * blockDim.x, first = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (size_t i = first; i < elements; i += stride) {
+        const float v = ElemIo<T>::load(buf + i);
+        for (int r = 0; r < tp; ++r) tp_store_tagged(peer_slots[r] + par + (size_t)rank * slot_stride + i, v, tag);
+    }
+    const unsigned long long *mine = peer_slots[rank] + par;
+    for (size_t i = first; i < elements; i += stride) {
+        float sum = 0.0f;
+        bool all_in = true;
+        for (int r = 0; r < tp && all_in; ++r) {
+            const unsigned long long *p = mine + (size_t)r * slot_stride + i;
+            float v = 0.0f;
+            bool in = tp_load_tagged(p, tag, &v);
+            for (uint32_t k = 0; !in && k < kTpPollLimit; ++k) {
+                __nanosleep(40);
+                in = tp_load_tagged(p, tag, &v);
+            }
+            all_in = in;
+            sum += v;
+        }
+        if (!all_in) { atomicCAS(status, 0u, 6u | ((unsigned)blockIdx.x << 8)); return; } /* 6 = a peer rank's data */
+        ElemIo<T>::store(buf + i, sum);
+    }
+}
+__global__ void tp_seq_advance_kernel(unsigned *seq_word) { *seq_word += 1u; }
+
+static int tp_allreduce_launch(TpComm *c, cudaStream_t stream, void *buffer, size_t elements, int dtype) {
+    if (!c->connected) return fail(FFN_ERR_STATE, "ffn_tp_allreduce_sum: the communicator is not connected");
+    if (dtype != 0 && dtype != 2) return fail(FFN_ERR_CONFIG, "ffn_tp_allreduce_sum: unknown element type %d (0 = f32, 2 = bf16)", dtype);
+    if (elements == 0) return FFN_OK;
+    if (!buffer) return fail(FFN_ERR_CONFIG, "ffn_tp_allreduce_sum: null buffer");
+    const size_t cap = (size_t)c->max_tokens * c->hidden;
+    if (elements > cap) return fail(FFN_ERR_CONFIG, "ffn_tp_allreduce_sum: %zu elements exceed the exchange slots (%zu)", elements, cap);
+    if (c->tp == 1) return FFN_OK;
+    unsigned *status = nullptr;
+    int st = fused_status_word(&status);
+    if (st) return st;
+    int sms = 0;
+    FFN_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device), "SM count");
+    const int threads = 256;
+    const int blocks = (int)min((size_t)sms * 4, (elements + threads - 1) / threads);
+    unsigned *seq = (unsigned *)(c->local + kTpSeqOffset);
+    if (dtype == 0)
+        tp_allreduce_kernel<float><<<blocks, threads, 0, stream>>>((float *)buffer, elements, c->d_slots, c->max_tokens * c->hidden, c->tp, c->rank, seq, status);
+    else
+        tp_allreduce_kernel<uint16_t><<<blocks, threads, 0, stream>>>((uint16_t *)buffer, elements, c->d_slots, c->max_tokens * c->hidden, c->tp, c->rank, seq, status);
+    FFN_CUDA_TRY(cudaGetLastError(), "ffn_tp_allreduce_sum launch");
+    tp_seq_advance_kernel<<<1, 1, 0, stream>>>(seq);
+    FFN_CUDA_TRY(cudaGetLastError(), "ffn_tp_allreduce_sum launch");
+    return FFN_OK;
+}
+
 }  // namespace ffn
 
 using namespace ffn;
@@ -186,6 +257,55 @@ int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *
     return st;
 }
 
+
+int ffn_tp_allreduce_sum(FfnTpComm *comm, void *stream, void *buffer, size_t elements, int dtype) {
+    clear_error();
+    TpComm *c = (TpComm *)comm;
+    if (!c) return fail(FFN_ERR_CONFIG, "ffn_tp_allreduce_sum: null communicator");
+    return tp_allreduce_launch(c, (cudaStream_t)stream, buffer, elements, dtype);
+}
+
+int ffn_allreduce_sum(FfnTpComm *const *comms, void *const *streams, int count, void *const *buffers, size_t elements,
+                      int dtype) {
+    clear_error();
+    if (count < 0 || !comms || !buffers) return fail(FFN_ERR_CONFIG, "ffn_allreduce_sum: null argument or negative count");
+    if (count <= 1 || elements == 0) return FFN_OK; /* as the reference: nothing to do */
+    for (int i = 0; i < count; ++i) {
+        TpComm *c = (TpComm *)comms[i];
+        if (!c || c->tp != count || c->rank != i) return fail(FFN_ERR_CONFIG, "ffn_allreduce_sum: element %d is not rank %d of %d", i, i, count);
+    }
+    int restore = 0;
+    (void)cudaGetDevice(&restore);
+    int st = FFN_OK;
+    for (int i = 0; i < count && !st; ++i) {
+        TpComm *c = (TpComm *)comms[i];
+        if (cudaSetDevice(c->device) != cudaSuccess) { st = fail(FFN_ERR_CUDA, "ffn_allreduce_sum: cannot select device %d", c->device); break; }
+        st = tp_allreduce_launch(c, streams ? (cudaStream_t)streams[i] : nullptr, buffers[i], elements, dtype);
+    }
+    (void)cudaSetDevice(restore);
+    return st;
+}
+
+int ffn_forward_mlp_host(FfnTpComm *comm, void *stream, const void *normed_host, void *layer_out_host, void *staging,
+                         void *ws, const FfnMlpWeights *w, int tokens, const FfnModelDims *dims) {
+    clear_error();
+    if (!dims || !w) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_host: null weights or dims");
+    if (!normed_host || !layer_out_host || !staging || !ws) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_host: null buffer");
+    const int limit = dims->max_chunk > 0 ? dims->max_chunk : 128;
+    if (tokens < 1 || tokens > limit) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_host: Layer token count exceeds the model's max_chunk");
+    if (dims->hidden_size <= 0) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_host: invalid hidden size");
+    const size_t bytes = (size_t)tokens * dims->hidden_size * 2;
+    cudaStream_t s = (cudaStream_t)stream;
+    uint16_t *x_dev = (uint16_t *)staging, *y_dev = x_dev + (size_t)tokens * dims->hidden_size;
+    FFN_CUDA_TRY(cudaMemcpyAsync(x_dev, normed_host, bytes, cudaMemcpyDefault, s), "ffn_forward_mlp_host: input copy");
+    TpComm *c = (TpComm *)comm;
+    const int st = (c && c->tp > 1) ? ffn_forward_mlp_tp(comm, stream, x_dev, ws, y_dev, w, tokens, dims, nullptr)
+                                    : ffn_forward_mlp_prepared(nullptr, stream, x_dev, ws, y_dev, w, tokens, dims);
+    if (st) return st;
+    FFN_CUDA_TRY(cudaMemcpyAsync(layer_out_host, y_dev, bytes, cudaMemcpyDefault, s), "ffn_forward_mlp_host: output copy");
+    FFN_CUDA_TRY(cudaStreamSynchronize(s), "ffn_forward_mlp_host: synchronize");
+    return FFN_OK;
+}
 
 /* One layer of the decode stack: h <- bf16(h + FFN(RMSNorm(h))) */
 static int decode_layer(TpComm *c, cudaStream_t stream, void *h, void *ws, void *layer_out, const FfnMlpWeights *w,

@@ -91,7 +91,16 @@ def _declare(lib):
         "ffn_convert_checkpoint": [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_char_p, ctypes.POINTER(ctypes.c_char_p), ci, ci],
         "ffn_json_reencode": [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_size_t],
         "ffn_verify_sidecar": [ctypes.c_char_p, ci, ctypes.c_char_p, ctypes.c_size_t],
+        "ffn_int4_noalloc_status": [ctypes.POINTER(ci), ctypes.POINTER(ci)],
+        "ffn_int4_describe_gemm_plan": [ci, ci, ci, ci, ci, ctypes.c_char_p, ctypes.c_size_t],
+        "ffn_forward_mlp_host": [vp, vp, vp, vp, vp, vp, ctypes.POINTER(MlpWeights), ci, ctypes.POINTER(ModelDims)],
+        "ffn_tp_allreduce_sum": [vp, vp, vp, ctypes.c_size_t, ci],
+        "ffn_allreduce_sum": [ctypes.POINTER(vp), ctypes.POINTER(vp), ci, ctypes.POINTER(vp), ctypes.c_size_t, ci],
     }
+    lib.ffn_tp_exchange_tag.argtypes = [ctypes.c_uint]
+    lib.ffn_tp_exchange_tag.restype = ctypes.c_uint
+    lib.ffn_int4_numerical_policy.argtypes = []
+    lib.ffn_int4_numerical_policy.restype = ctypes.c_char_p
     lib.ffn_quant_manifest_free.argtypes = [vp]
     lib.ffn_quant_manifest_free.restype = None
     lib.ffn_host_free.argtypes = [vp]

@@ -10,6 +10,14 @@
  * default stream).  There is no CPU fallback: without a usable CUDA device every compute entry
  * point fails with FFN_ERR_CUDA.
  *
+ * Concurrency: the FFN entry points of one device (ffn_forward_mlp*, ffn_forward_mlp_tp,
+ * ffn_decode_stack, ffn_gemm_int4_bf16 with one or two rows, ffn_tp_allreduce_sum) share that
+ * device's synchronisation words, kernel status word and, for 3..64 tokens, one scratch region
+ * (permuted activations, split-K partial sums, arrival counters).  Calls on one device must
+ * therefore be serialised: issue them on one stream, or order the streams with events.  Calls on
+ * different devices are independent.  The first call on a device, and the first call of the batched
+ * path there, allocate these words with cudaMalloc: make them before capturing a CUDA graph.
+ *
  * Data layouts (identical to the reference's, csrc/include/linear_weight.h:12-13, 46-54):
  *   packed [N][K/2]   u8, row-major; byte j of a row = code(k=2j) | code(k=2j+1) << 4; codes are
  *                     4-bit two's complement in [-7, 7]; 0x8 is the reserved invalid code
@@ -51,6 +59,24 @@ int ffn_int4_abi_version(void);
  * (csrc/engine.cu:1723-1730).  No counterpart function in the reference. */
 int ffn_int4_device_status(int *where, int *cta);
 
+/* The same report for ffn_forward_mlp_prepared_noalloc, whose kernel keeps its status word inside
+ * the library's static scratch array: synchronises the current device, copies the word to the host
+ * and, when it is non-zero, clears it together with the array's synchronisation words.  Calls no
+ * allocating routine, so a host that cannot allocate can use it (ffn_int4_device_status allocates
+ * the regular path's words on first use; it also reports this word once the array is in use on the
+ * device).  A wait that ran out stays on record across later calls until one of the two functions
+ * reads it.  No counterpart in the reference. */
+int ffn_int4_noalloc_status(int *where, int *cta);
+
+/* The identity of this library's arithmetic for the reference's execution manifest: the members it
+ * contributes to the `numerical_policy` fields (csrc/manifest.c:385-434), as text of the form
+ * "key":"value","key":"value" with sorted keys.  `weight_quantization` carries the reference's own
+ * value for INT4 operands (csrc/manifest.c:433-434, set at csrc/engine.cu:1357); the other members
+ * name the accumulation scheme, the rounding points and the cross-rank reduction, so that
+ * numerical_policy_id moves when the engine is linked against this library and semantic_id /
+ * deployment_id do not (the property tests/manifest_test.c:335-352 checks for the INT4 switch). */
+const char *ffn_int4_numerical_policy(void);
+
 /* Which kernel a call of this shape takes and its launch geometry (grid, shared memory, pipeline
  * stages, tile sizes, K splits), as one line of key=value text, for a device with `sm_count` SMs and
  * `smem_optin` bytes of opt-in shared memory per block.  Pure host arithmetic: needs no GPU, so the
@@ -58,6 +84,8 @@ int ffn_int4_device_status(int *where, int *cta);
  * counterpart in the reference (its launch shapes are fixed constants, csrc/kernels/gemm_quant.cu:20-31). */
 int ffn_int4_describe_plan(int tokens, int hidden, int intermediate, int sm_count, int smem_optin, char *out,
                            size_t out_bytes);
+/* The same for one ffn_gemm_int4_bf16 call of m rows against an [n][k] matrix. */
+int ffn_int4_describe_gemm_plan(int m, int n, int k, int sm_count, int smem_optin, char *out, size_t out_bytes);
 
 /* Debugging aid: when given a device buffer of 16 int64, CTA 0 of every later fused launch writes
  * clock64() stamps of its pipeline events there (NULL switches it off).  No counterpart in the
@@ -80,7 +108,10 @@ int ffn_int4_set_fused(int enabled);
  * negative extent, K <= 0, group <= 0, null buffer, K not a whole number of groups; this
  * library additionally requires group == 128 (the only group the format defines,
  * csrc/linear_weight.cpp:63-68).  M == 0 or N == 0 is a successful no-op.  Asynchronous on
- * `stream`. */
+ * `stream`.  One or two rows (the decode case: the FFN's matrices on their own, attention / GDN
+ * projections, the LM head) stream through the persistent bulk-copy kernel when N % 8 == 0, K <=
+ * 34816 (17408 for two rows) and the three operands are 16-byte aligned; everything else takes the
+ * shape-generic kernel.  A non-finite activation makes the outputs it reaches non-finite in both. */
 int ffn_gemm_int4_bf16(const void *a, const void *packed, const void *scales, void *out, int M,
                        int N, int K, int group, void *stream);
 
@@ -121,10 +152,12 @@ int ffn_residual_add(void *dst, const void *src, int n, void *stream);
 int ffn_quantize_int4(const void *weights, void *packed, void *scales, long long n, long long k, void *stream);
 
 /* Writes float(code) * float(scale) for every element of a packed [N][K] weight to out (FP32
- * [N][K]) using the same unpack routine the GEMV kernels use.  Exists so the "dequantized
- * weights are bit-exact" bar can be checked against linear_dequantize_int4
- * (csrc/linear_weight.cpp:178-216).  `bad` (device int, may be NULL) receives the number of
- * reserved 0x8 nibbles met. */
+ * [N][K]), so that the "dequantized weights are bit-exact" bar can be checked against
+ * linear_dequantize_int4 (csrc/linear_weight.cpp:178-216).  It uses the shape-generic kernel's
+ * unpack routine; the streaming and the tensor-core kernels widen the codes in their own ways, which
+ * the tests pin separately with one-hot activations (a single non-zero activation makes their
+ * arithmetic exact, so their outputs must then equal code * scale * activation bit for bit).
+ * `bad` (device int, may be NULL) receives the number of reserved 0x8 nibbles met. */
 int ffn_dequantize_int4(void *out, const void *packed, const void *scales, int N, int K, int *bad,
                         void *stream);
 
@@ -203,7 +236,9 @@ int ffn_forward_mlp_prepared(void *cublas, void *stream, const void *normed, voi
  * first call before any stream capture.  All calls on a device share the one array and it keeps the
  * last call's contents: the words that must start at zero are cleared on `stream` at the start of
  * every call, and two calls that overlap on the GPU (different streams) race - serialise them.
- * Kernel status words of this entry point are not the ones ffn_int4_device_status reads.
+ * A bounded wait that ran out inside this entry point's kernel is reported by
+ * ffn_int4_noalloc_status (which allocates nothing either); the status word is not cleared between
+ * calls, so the report is not lost when further calls follow.
  * This entry point has no counterpart in the reference. */
 int ffn_forward_mlp_prepared_noalloc(void *stream, const void *normed, void *layer_out,
                                      const FfnMlpWeights *w, int tokens, const FfnModelDims *dims);
@@ -238,10 +273,42 @@ int ffn_tp_destroy(FfnTpComm *comm);
  * residual = bf16(f32(residual) + f32(layer_out)) (residual_add_device, csrc/engine.cu:1428-1433).
  * Every rank must make the same sequence of calls, each within about a second of the others; a rank
  * that never launches makes the others return after that bounded wait with a status
- * ffn_int4_device_status reports.  1 or 2 tokens run the single-launch kernel, 3..64 the tensor-core
+ * ffn_int4_device_status reports; after such a report the ranks' call counters may differ, so every
+ * rank must either have made the same number of calls or destroy and recreate its communicator.  1 or 2 tokens run the single-launch kernel, 3..64 the tensor-core
  * pair (exchange in the down launch's epilogue); more are refused with FFN_ERR_CONFIG. */
 int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *ws, void *layer_out,
                        const FfnMlpWeights *w, int tokens, const FfnModelDims *dims, void *residual);
+
+/* The operator call for a caller whose activations live in HOST memory (the engine ABI's callers
+ * pass host buffers, csrc/include/engine.h:11-12): copies normed_host [tokens][H] bf16 into
+ * `staging`, runs ffn_forward_mlp_prepared (comm == NULL or one rank) or ffn_forward_mlp_tp on
+ * `stream`, copies the result back to layer_out_host and synchronises the stream once - one call
+ * instead of copy, launch, copy, synchronise issued separately.  `staging` is 2*tokens*H bf16 of
+ * device memory owned by the caller; host buffers should be pinned (pageable memory works, through
+ * the driver's staging).  Either host pointer may also be a device pointer.  No counterpart in the
+ * reference (its decode step keeps activations on the device between sublayers). */
+int ffn_forward_mlp_host(FfnTpComm *comm, void *stream, const void *normed_host, void *layer_out_host,
+                         void *staging, void *ws, const FfnMlpWeights *w, int tokens, const FfnModelDims *dims);
+
+/* Replaces allreduce_sum (csrc/include/layers.h:303-305; csrc/collective.cu:168-219) as a separate
+ * collective, for the engine's other sharded sublayers and as the comparison arm of the fused
+ * reduce: in-place elementwise sum of one buffer per rank over the communicator's exchange slots
+ * (every rank pushes its elements into every rank's memory over NVLink, waits - bounded - for the
+ * others', adds the tp values in rank order in FP32 and rounds once; the reference's leader adds
+ * pairwise and rounds after every add).  dtype: 0 = float, 2 = bf16 (the values of COLLECTIVE_F32 /
+ * COLLECTIVE_BF16, layers.h:272-278); other element types are refused with FFN_ERR_CONFIG as the
+ * reference refuses unknown types.  `elements` may not exceed max_tokens * hidden of the communicator.
+ * One rank per call; every rank makes the same call. */
+int ffn_tp_allreduce_sum(FfnTpComm *comm, void *stream, void *buffer, size_t elements, int dtype);
+/* The same for a process that drives every rank, in allreduce_sum's shape: comms[i], streams[i]
+ * (may be NULL: default streams) and buffers[i] are index-aligned, comms[i] being rank i of `count`.
+ * The reference's producer / done events and its leader staging buffer have no role here (ordering
+ * is stream order, data goes straight into the peers' slots).  The caller synchronises afterwards. */
+int ffn_allreduce_sum(FfnTpComm *const *comms, void *const *streams, int count, void *const *buffers,
+                      size_t elements, int dtype);
+/* The tag the exchange words of call number `call_number` carry (never zero, also across the wrap
+ * of the 32-bit call counter).  Exported for tests; no counterpart in the reference. */
+unsigned ffn_tp_exchange_tag(unsigned call_number);
 
 /* The decode stack's FFN sublayers with identity mixers: for l in 0..num_layers-1,
  *     h <- bf16( f32(h) + f32( FFN_l( RMSNorm_l(h) ) ) )
