@@ -1,6 +1,9 @@
 """Builds libffn_int4.so in-tree with nvcc for sm_100a (no JIT cache, no torch extension).
 
-    python haskell-infer-demo_b200/build.py [--force] [--verbose]
+    python haskell-infer-demo_b200/build.py [--force] [--verbose] [--tuning]
+
+--tuning compiles the measurement switches in (-DFFN_INT4_TUNING: the FFN_INT4_DEBUG and
+FFN_INT4_STAGE_KB environment variables are then read); the default build has none of them.
 
 The library is plain CUDA C++ behind a C ABI (include/ffn_int4.h); PyTorch is not linked.
 """
@@ -17,7 +20,7 @@ FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std
 
 
 def sources():
-    return sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "host", "*.c")))
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
 def stale():
@@ -25,13 +28,12 @@ def stale():
         return True
     built = os.path.getmtime(OUT)
     deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.h")) + \
-        glob.glob(os.path.join(CSRC, "host", "*.h")) + \
         glob.glob(os.path.join(HERE, "..", "include", "*.h"))
     return any(os.path.getmtime(d) > built for d in deps)
 
 
-def build(force=False, verbose=False):
-    if not force and not stale():
+def build(force=False, verbose=False, tuning=False):
+    if not force and not tuning and not stale():
         return OUT
     objs = []
     objdir = os.path.join(HERE, "build")
@@ -40,9 +42,7 @@ def build(force=False, verbose=False):
     for src in sources():
         obj = os.path.join(objdir, os.path.basename(src) + ".o")
         objs.append(obj)
-        cmd = [NVCC] + FLAGS + ["-Xcompiler", "-fPIC", "-c", src, "-o", obj]
-        if src.endswith(".c"):
-            cmd = [NVCC, "-O2", "-Xcompiler", "-fPIC", "-x", "c", "-c", src, "-o", obj]
+        cmd = [NVCC] + FLAGS + (["-DFFN_INT4_TUNING"] if tuning else []) + ["-Xcompiler", "-fPIC", "-c", src, "-o", obj]
         if verbose:
             cmd[1:1] = ["-Xptxas", "-v"]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -60,4 +60,4 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, tuning="--tuning" in sys.argv))

@@ -33,6 +33,13 @@ struct TpComm {
     bool connected = false;
 };
 
+/* Puts the calling thread's current device back when a function that switches devices returns. */
+struct DeviceRestore {
+    int dev = -1;
+    DeviceRestore() { if (cudaGetDevice(&dev) != cudaSuccess) { dev = -1; (void)cudaGetLastError(); } }
+    ~DeviceRestore() { if (dev >= 0) (void)cudaSetDevice(dev); }
+};
+
 static int tp_publish_tables(TpComm *c) {
     unsigned long long *slots[kTpMaxRanks];
     for (int r = 0; r < c->tp; ++r) slots[r] = (unsigned long long *)(c->peer[r] + kTpHeaderBytes);
@@ -164,6 +171,7 @@ int ffn_tp_connect(FfnTpComm *comm, const void *all_handles) {
     TpComm *c = (TpComm *)comm;
     if (!c || !all_handles) return fail(FFN_ERR_CONFIG, "ffn_tp_connect: null argument");
     if (c->connected) return fail(FFN_ERR_STATE, "ffn_tp_connect: already connected");
+    DeviceRestore restore_device;
     FFN_CUDA_TRY(cudaSetDevice(c->device), "ffn_tp_connect: select device");
     for (int r = 0; r < c->tp; ++r) {
         if (r == c->rank) continue;
@@ -189,8 +197,7 @@ int ffn_tp_connect_local(FfnTpComm *const *comms, int count) {
         TpComm *c = (TpComm *)comms[i];
         if (!c || c->tp != count || c->rank != i) return fail(FFN_ERR_CONFIG, "ffn_tp_connect_local: element %d is not rank %d of %d", i, i, count);
     }
-    int restore = 0;
-    (void)cudaGetDevice(&restore);
+    DeviceRestore restore_device;
     for (int i = 0; i < count; ++i) {
         TpComm *c = (TpComm *)comms[i];
         FFN_CUDA_TRY(cudaSetDevice(c->device), "ffn_tp_connect_local: select device");
@@ -209,7 +216,6 @@ int ffn_tp_connect_local(FfnTpComm *const *comms, int count) {
         const int st = tp_publish_tables(c);
         if (st) return st;
     }
-    (void)cudaSetDevice(restore);
     return FFN_OK;
 }
 
@@ -217,6 +223,7 @@ int ffn_tp_destroy(FfnTpComm *comm) {
     clear_error();
     TpComm *c = (TpComm *)comm;
     if (!c) return FFN_OK;
+    DeviceRestore restore_device;
     (void)cudaSetDevice(c->device);
     (void)cudaDeviceSynchronize();
     for (int r = 0; r < c->tp; ++r)
@@ -274,15 +281,13 @@ int ffn_allreduce_sum(FfnTpComm *const *comms, void *const *streams, int count, 
         TpComm *c = (TpComm *)comms[i];
         if (!c || c->tp != count || c->rank != i) return fail(FFN_ERR_CONFIG, "ffn_allreduce_sum: element %d is not rank %d of %d", i, i, count);
     }
-    int restore = 0;
-    (void)cudaGetDevice(&restore);
+    DeviceRestore restore_device;
     int st = FFN_OK;
     for (int i = 0; i < count && !st; ++i) {
         TpComm *c = (TpComm *)comms[i];
         if (cudaSetDevice(c->device) != cudaSuccess) { st = fail(FFN_ERR_CUDA, "ffn_allreduce_sum: cannot select device %d", c->device); break; }
         st = tp_allreduce_launch(c, streams ? (cudaStream_t)streams[i] : nullptr, buffers[i], elements, dtype);
     }
-    (void)cudaSetDevice(restore);
     return st;
 }
 

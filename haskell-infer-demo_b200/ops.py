@@ -210,3 +210,23 @@ def decode_stack(mlps, h, comm=None, ws=None, layer_out=None):
     check(load().ffn_decode_stack(comm.handle if comm is not None else None, _stream(), _ptr(h), _ptr(ws),
                                   _ptr(layer_out), arr, len(mlps), tokens, ctypes.byref(first.dims)))
     return h
+
+
+def forward_mlp_host(mlp, normed_host, layer_out_host, staging, ws, comm=None):
+    """One FFN for activations in (pinned) HOST memory: copy in, FFN, copy out and one stream
+    synchronisation inside a single library call (include/ffn_int4.h, ffn_forward_mlp_host).
+    ``staging`` is device memory for 2*T*H bf16; ``comm`` a TpComm (None = TP 1)."""
+    tokens = normed_host.shape[0]
+    check(load().ffn_forward_mlp_host(comm.handle if comm is not None else None, _stream(),
+                                      ctypes.c_void_p(normed_host.data_ptr()), ctypes.c_void_p(layer_out_host.data_ptr()),
+                                      _ptr(staging), _ptr(ws), ctypes.byref(mlp.weights), tokens, ctypes.byref(mlp.dims)))
+    return layer_out_host
+
+
+def tp_allreduce_sum(comm, buffer):
+    """In-place sum of ``buffer`` (bf16 or fp32, at most max_tokens*hidden elements) over the ranks of
+    ``comm`` through the exchange slots (include/ffn_int4.h, ffn_tp_allreduce_sum)."""
+    _require_cuda(buffer)
+    dtype = {torch.float32: 0, torch.bfloat16: 2}[buffer.dtype]
+    check(load().ffn_tp_allreduce_sum(comm.handle, _stream(), _ptr(buffer), buffer.numel(), dtype))
+    return buffer

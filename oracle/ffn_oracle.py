@@ -231,13 +231,20 @@ def ffn(layer: Layer, x: np.ndarray, accumulate="f64", intermediates=False):
     only to measure how far two legitimate oracles drift apart on a deep stack).
     """
     x = np.ascontiguousarray(x, dtype=np.float32)
-    if accumulate == "f64":
+    # many tokens: the same FP64 sums through BLAS on the dequantized weights (the C loop over the
+    # packed bytes is single-threaded); a few tokens: straight from the packed bytes
+    blas = accumulate == "f64" and x.shape[0] > 4
+    if blas:
+        gu = matmul_f64(x, dequantize(layer.gate_up_packed, layer.gate_up_scales))
+    elif accumulate == "f64":
         gu = matmul_packed_f64(x, layer.gate_up_packed, layer.gate_up_scales)
     else:
         gu = x @ dequantize(layer.gate_up_packed, layer.gate_up_scales).T
     gu = bf16_round(gu.astype(np.float32))
     act = silu_mul(gu[:, :layer.inter], gu[:, layer.inter:])
-    if accumulate == "f64":
+    if blas:
+        y = matmul_f64(act, dequantize(layer.down_packed, layer.down_scales))
+    elif accumulate == "f64":
         y = matmul_packed_f64(act, layer.down_packed, layer.down_scales)
     else:
         y = act @ dequantize(layer.down_packed, layer.down_scales).T

@@ -1,5 +1,7 @@
 """Helpers shared by the GPU parity tests: moving oracle arrays to the device and the
 acceptance bars."""
+import os
+
 import numpy as np
 import torch
 
@@ -44,14 +46,26 @@ def bf16_ulp(values):
     return np.exp2(e - 7).astype(np.float32)
 
 
-def assert_ffn_close(got, want, what=""):
-    """The stated bars: relative L2 <= 5e-3 and max-abs <= 2e-2.  Where one BF16 ulp of the
-    expected value is itself larger than 2e-2 (|y| >= 4: two FP32/FP64-accumulating CPU oracles
-    already differ there by one ulp on a handful of elements), the element bar is one ulp."""
+def ffn_error_report(got, want):
+    """Every figure of the comparison: max-abs, relative L2, how many elements exceed the plain 2e-2
+    bar (they are admitted only where one BF16 ulp of the expected value is larger than 2e-2), and how
+    far the worst element is above max(2e-2, 1 ulp)."""
     max_abs, rel = o.compare(got, want)
     err = np.abs(got.astype(np.float64) - want.astype(np.float64))
     bar = np.maximum(MAX_ABS, bf16_ulp(want).astype(np.float64))
-    worst = float((err - bar).max())
-    assert rel <= REL_L2, f"{what}: relative L2 {rel:.3g} > {REL_L2}"
-    assert worst <= 0, f"{what}: max-abs {max_abs:.3g} exceeds max(2e-2, 1 BF16 ulp)"
-    return max_abs, rel
+    return {"max_abs": max_abs, "rel_l2": rel, "over_2e-2": int(np.count_nonzero(err > MAX_ABS)),
+            "ulp_excess": float(max(0.0, (err - bar).max())) if err.size else 0.0, "elements": int(err.size)}
+
+
+def assert_ffn_close(got, want, what=""):
+    """The stated bars: relative L2 <= 5e-3 and max-abs <= 2e-2.  Where one BF16 ulp of the
+    expected value is itself larger than 2e-2 (|y| >= 4: two FP32/FP64-accumulating CPU oracles
+    already differ there by one ulp on a handful of elements), the element bar is one ulp.  The
+    strict figures are printed, so a run shows how many elements used that allowance."""
+    r = ffn_error_report(got, want)
+    if os.environ.get("RANK", "0") == "0":      # one line per check, not one per rank
+        print(f"{what}: max-abs {r['max_abs']:.3g} rel-L2 {r['rel_l2']:.3g}; {r['over_2e-2']} of {r['elements']} elements "
+              f"above the plain 2e-2 bar (all within one BF16 ulp: {r['ulp_excess'] == 0})")
+    assert r["rel_l2"] <= REL_L2, f"{what}: relative L2 {r['rel_l2']:.3g} > {REL_L2}"
+    assert r["ulp_excess"] <= 0, f"{what}: max-abs {r['max_abs']:.3g} exceeds max(2e-2, 1 BF16 ulp)"
+    return r["max_abs"], r["rel_l2"]

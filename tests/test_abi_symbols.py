@@ -92,3 +92,59 @@ def test_compute_entries_fail_loudly_without_a_gpu():
     d.hidden_size, d.intermediate_size, d.max_chunk, d.rms_eps = 128, 128, 128, 1e-6
     assert lib.ffn_forward_mlp_prepared(None, None, p, p, p, ctypes.byref(w), 1, ctypes.byref(d)) < 0
     assert lib.ffn_int4_last_error()
+    assert lib.ffn_forward_mlp_prepared_noalloc(None, p, p, ctypes.byref(w), 1, ctypes.byref(d)) < 0
+    assert lib.ffn_int4_noalloc_status(None, None) < 0 and lib.ffn_int4_last_error()
+    assert lib.ffn_forward_mlp_host(None, None, p, p, p, p, ctypes.byref(w), 1, ctypes.byref(d)) < 0
+
+
+def test_exchange_tag_is_never_zero_across_the_counter_wrap():
+    """A zero tag means "nobody wrote this word since the buffer was cleared", so no call number may
+    map to it - also not the last value of the 32-bit call counter."""
+    lib = L.load()
+    for call in (0, 1, 2, 0x7FFFFFFF, 0x80000000, 0xFFFFFFFD, 0xFFFFFFFE, 0xFFFFFFFF):
+        assert lib.ffn_tp_exchange_tag(call) != 0
+    # consecutive calls use the two slot parities alternately, so equal tags on calls n and n+1 are harmless;
+    # calls n and n+2 (the same slots) must differ
+    for call in (0, 5, 0xFFFFFFFD, 0xFFFFFFFE, 0xFFFFFFFF):
+        assert lib.ffn_tp_exchange_tag(call) != lib.ffn_tp_exchange_tag((call + 2) & 0xFFFFFFFF)
+
+
+def test_new_host_side_validation_and_identity():
+    import ctypes
+    lib = L.load()
+    fields = lib.ffn_int4_numerical_policy().decode()
+    import json
+    parsed = json.loads("{" + fields + "}")
+    assert list(parsed) == sorted(parsed)                     # sorted keys, as the manifest emitter writes them
+    assert parsed["weight_quantization"] == "int4_symmetric_group_bf16_scale_decode_only"   # csrc/manifest.c:433-434
+    assert lib.ffn_tp_allreduce_sum(None, None, None, 4, 2) == -4
+    assert lib.ffn_allreduce_sum(None, None, 2, None, 4, 2) == -4
+    assert lib.ffn_allreduce_sum(None, None, 1, None, 4, 2) == -4      # null arrays are refused before the count is looked at
+    w, d = L.MlpWeights(), L.ModelDims()
+    assert lib.ffn_forward_mlp_host(None, None, None, None, None, None, ctypes.byref(w), 1, ctypes.byref(d)) == -4
+    buf = ctypes.create_string_buffer(512)
+    assert lib.ffn_int4_describe_gemm_plan(1, 4096, 5120, 148, 232448, buf, 512) == 0 and b"stream_gemv" in buf.value
+    assert lib.ffn_int4_describe_gemm_plan(1, 4100, 5120, 148, 232448, buf, 512) == 0 and b"generic" in buf.value   # N % 8
+    assert lib.ffn_int4_describe_gemm_plan(2, 4096, 34816, 148, 232448, buf, 512) == 0 and b"generic" in buf.value  # two rows: K <= 17408
+    assert lib.ffn_int4_describe_gemm_plan(1, 4096, 192, 148, 232448, buf, 512) == -4
+
+
+def test_header_conforms_to_the_reference_headers_where_a_checkout_exists():
+    """Compile-only: include/ffn_int4.h against the reference's layers.h / engine.h (field offsets of
+    both struct mirrors, status codes, prototypes), as the reference's engine stub includes engine.h so
+    that drift breaks the build (tests/generation_engine_stub.c:1-12)."""
+    import subprocess
+    import sys
+
+    import pytest
+    sys.path.insert(0, ROOT)
+    from __graft_entry__ import reference_checkout
+    ref = reference_checkout()
+    if not ref:
+        pytest.skip("no reference checkout on this machine")
+    obj = os.path.join(ROOT, "oracle", "_ref", "abi_conformance.o")
+    if os.path.exists(obj):
+        os.remove(obj)
+    proc = subprocess.run(["make", "-C", os.path.join(ROOT, "oracle"), f"REFERENCE={ref}", "_ref/abi_conformance.o"],
+                          capture_output=True, text=True)
+    assert proc.returncode == 0 and os.path.exists(obj), proc.stdout + proc.stderr

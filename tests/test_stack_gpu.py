@@ -13,7 +13,7 @@ import torch
 from haskell_infer_demo_b200 import lib as L
 from haskell_infer_demo_b200.ops import decode_stack
 from oracle import ffn_oracle as o
-from gpu_util import assert_ffn_close, dev_bf16, host_f32, upload_layer
+from gpu_util import assert_ffn_close, dev_bf16, dev_bits, host_f32, upload_layer
 
 pytestmark = pytest.mark.gpu
 
@@ -59,3 +59,67 @@ def test_stack_refusals(cuda):
     mlp = upload_layer(layers[0], cuda)            # no post-norm weight
     with pytest.raises(FfnError, match="post-norm"):
         decode_stack([mlp], dev_bf16(h0, cuda).clone())
+
+
+def load_stack_golden():
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "stack_cfg4.npz")
+    if not os.path.exists(path):
+        pytest.skip("tests/golden/stack_cfg4.npz has not been generated (tests/golden/make_stack_golden.py)")
+    return np.load(path)
+
+
+def check_stack_against_golden(dev, mlps, golden, comm=None, sync=None, what=""):
+    """Teacher-forced and free-running gates of the 64-layer 27B-shape stack for one rank's operands
+    `mlps` (shared by the single-GPU test and the tensor-parallel worker).  `sync` is called before every
+    launch that other ranks must join within the kernels' bounded waits."""
+    from haskell_infer_demo_b200 import synth
+    nl, hidden, inter, tokens8, seed = [int(v) for v in golden["shape"]]
+    sync = sync or (lambda: None)
+    x8 = synth.stack_input_torch(seed, tokens8, hidden, dev)
+    tok0 = o.bf16_to_f32(golden["tok0_states"])
+    # (i) teacher-forced, one token, every layer: input = the oracle's state before the layer
+    worst = 0.0
+    for l in range(nl):
+        h = (x8[:1] if l == 0 else dev_bf16(tok0[l - 1:l], dev)).clone()
+        sync()
+        decode_stack([mlps[l]], h, comm=comm)
+        L.device_status()
+        worst = max(worst, assert_ffn_close(host_f32(h), tok0[l:l + 1], f"{what} layer {l} teacher-forced, M=1")[1])
+    # eight tokens on the kept layers
+    for j, l in enumerate(int(v) for v in golden["m8_layers"]):
+        h = dev_bits(golden["m8_states"][j, 0], dev).clone()
+        sync()
+        decode_stack([mlps[l]], h, comm=comm)
+        L.device_status()
+        assert_ffn_close(host_f32(h), o.bf16_to_f32(golden["m8_states"][j, 1]), f"{what} layer {l} teacher-forced, M=8")
+    # (ii) free-running final state against the oracle-vs-oracle spread
+    spread = float(golden["spread_rel_l2"])
+    want = o.bf16_to_f32(golden["final_f64"])
+    out = {}
+    for m in (1, 8):
+        h = x8[:m].clone()
+        sync()
+        decode_stack(mlps, h, comm=comm)
+        L.device_status()
+        rel = o.compare(host_f32(h), want[:m])[1]
+        out[m] = (rel, h)
+        print(f"{what} 64-layer stack M={m}: free-running rel-L2 {rel:.3g} (FP32- vs FP64-accumulating CPU oracles: {spread:.3g}); "
+              f"worst teacher-forced layer rel-L2 {worst:.3g}")
+        assert rel <= max(5e-3, 2 * spread)
+    return out
+
+
+def test_stack_27b_shape_64_layers_against_golden(cuda):
+    """BASELINE configs[4] at its full shape on one GPU: 64 independently generated layers (H=5120,
+    I=17408), checked against the committed CPU-oracle trajectory."""
+    from haskell_infer_demo_b200 import synth
+    golden = load_stack_golden()
+    nl, hidden, inter, _, seed = [int(v) for v in golden["shape"]]
+    mlps = [synth.stack_layer_torch(seed, l, hidden, inter, 1, 0, cuda) for l in range(nl)]
+    # the device-side generator and quantizer reproduce the CPU side's bytes
+    import hashlib
+    t = mlps[0].tensors
+    got = ",".join(hashlib.sha256(a.cpu().numpy().tobytes()).hexdigest() for a in (t[0], t[1].view(torch.int16), t[2], t[3].view(torch.int16)))
+    assert got == str(golden["digest_layer0"])
+    check_stack_against_golden(cuda, mlps, golden, what="TP=1")
