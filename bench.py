@@ -124,7 +124,7 @@ def _compare(got, want, rel_bar=5e-3):
             "rel_l2_bar": rel_bar, "ok": bool(rel <= rel_bar and excess <= 0.0)}
 
 
-def parity_single_layer(dev, comm, tp, rank, h, i, m, use_nccl):
+def parity_single_layer(dev, comm, tp, rank, h, i, m, use_nccl, kmajor):
     """One more call of the timed entry point, on the oracle's seeded data of the same shape
     (numpy default_rng: seed 2 up to two tokens as BASELINE configs[2], seed 3 beyond as configs[3]),
     this rank's slice cut by the oracle's slicer, compared with the TP=1 CPU oracle."""
@@ -143,6 +143,8 @@ def parity_single_layer(dev, comm, tp, rank, h, i, m, use_nccl):
         return torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).to(dev).view(torch.bfloat16)
 
     mlp = DenseMlp(torch.from_numpy(gp).to(dev), bits(gs), torch.from_numpy(dp).to(dev), bits(ds))
+    if kmajor:
+        mlp.prepare()
     xd = bits(o.bf16_bits(xs))
     torch.cuda.synchronize()
     if tp > 1:
@@ -228,6 +230,9 @@ def run_ours(args):
         copies = max(2, int(2.2 * L2_BYTES / per_rank_bytes) + 1)
         layers = [synth.stack_layer_torch(2, c, h, i, tp, rank, dev, with_norm=False) for c in range(copies)]
         x = synth.stack_input_torch(2, m, h, dev)
+    if not args.row_major:  # k-major copies of the down projections: the decode kernel without the phase barrier
+        for lay in layers:
+            lay.prepare()
     use_nccl = world > 1 and args.exchange == "nccl"
     if use_nccl and stack:
         raise SystemExit("--exchange nccl is a single-layer comparison; drop --layers")
@@ -347,7 +352,7 @@ def run_ours(args):
     parity = None
     if not args.no_parity:
         parity = parity_stack(dev, layers, comm, tp, h, i, m, x) if stack else \
-            parity_single_layer(dev, comm, tp, rank, h, i, m, use_nccl)
+            parity_single_layer(dev, comm, tp, rank, h, i, m, use_nccl, not args.row_major)
         if world > 1 and parity.get("ok") is not None:
             flag = torch.tensor([1 if parity["ok"] else 0], device=dev)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
@@ -366,6 +371,9 @@ def run_ours(args):
         peak, peak_kind = measured_peak_gbs()
         gbs = nl * per_rank_bytes / us_step / 1e3
         per_layer = 1 if m <= 2 else (4 if stack else 3)
+        launches = nl * per_layer
+        if stack and m <= 2 and not args.row_major:
+            launches = -(-nl // 64)          # the whole stack in one persistent launch per 64 layers
         line = {
             "metric": METRIC, "value": round(us_step, 3), "unit": "us/step", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(us_step / 1e3, 6),
@@ -381,11 +389,13 @@ def run_ours(args):
                        "timing": f"{args.steps} steps in one CUDA graph, median of {reps} replays, max over ranks"},
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(gbs / peak, 4), "peak_source": peak_kind, "traffic": captured_traffic(tp, m, args.layers),
-                         "algorithmic_bytes_per_launch": per_rank_bytes, "launches_per_step": nl * per_layer},
+                         "algorithmic_bytes_per_launch": per_rank_bytes * nl / launches, "launches_per_step": launches},
             "e2e": {"value": round(e2e_us, 3), "unit": "us/step", "h2d_bytes_per_step": m * h * 2,
                     "d2h_bytes_per_step": m * h * 2,
                     "through": "ffn_forward_mlp_host" if not (stack or use_nccl) else "copy, call, copy, synchronise issued by the caller"},
-            "gpu_launches": args.steps * nl * per_layer,
+            "gpu_launches": args.steps * launches,
+            "kernel": ("k-major decode kernel (persistent, no phase barrier)" if (m <= 2 and not args.row_major) else
+                       "row-major single-launch kernel" if m <= 2 else "tensor-core pair (mma.sync)"),
             "exchange": ("none (one GPU)" if world == 1 else "in-kernel tagged-word exchange over NVLink peer memory"
                          if not use_nccl else "comparison variant: NCCL all-reduce of the BF16 output after the kernel"),
             "parity": parity,
@@ -534,6 +544,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle comparison of the timed workload")
+    ap.add_argument("--row-major", action="store_true",
+                    help="do not register k-major copies of the down projections: one or two tokens then run the row-major "
+                         "single-launch kernel (one launch per layer)")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1 only. fused: the cross-rank sum inside the FFN kernel (the product). nccl: comparison "
                          "variant - the same kernel per rank without an exchange, then an NCCL all-reduce of the BF16 "

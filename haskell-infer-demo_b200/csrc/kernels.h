@@ -89,6 +89,15 @@ int fused_status_noalloc(unsigned *status_out, bool reset);
 bool fused_noalloc_in_use();
 bool gemv_describe_plan(int tokens, int N, int K, int sm_count, int smem_optin, char *out, size_t out_bytes);
 void fused_set_trace(long long *device_buffer);
+/* ffn_kmajor.cu: the persistent multi-layer kernel over k-major copies of the down projections
+ * (registered per layer with ffn_decode_layer_prepare).  `layers` are `num_layers` consecutive layers
+ * of one stack (1 for a single FFN call); with_norm fuses each layer's RMSNorm (post_norm_w) into its
+ * input stage.  FFN_NOT_ADMITTED when a layer is not registered or the shape is outside the kernel. */
+int kmajor_ffn_launch(cudaStream_t stream, const void *x, void *act, void *layer_out, const FfnMlpWeights *layers,
+                      int num_layers, int tokens, int H, int I, const FusedTp *tp, void *residual, int with_norm,
+                      float eps, int gemma, unsigned *status);
+void kmajor_reset_sync();
+bool kmajor_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin, char *out, size_t out_bytes);
 /* ffn_mma.cu: the tensor-core path for 3..64 tokens (two launches: gate/up + SiLU*up, down + reduce). */
 int mma_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                    const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual, unsigned *status);

@@ -301,13 +301,27 @@ int ffn_forward_mlp_host(FfnTpComm *comm, void *stream, const void *normed_host,
     if (dims->hidden_size <= 0) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_host: invalid hidden size");
     const size_t bytes = (size_t)tokens * dims->hidden_size * 2;
     cudaStream_t s = (cudaStream_t)stream;
-    uint16_t *x_dev = (uint16_t *)staging, *y_dev = x_dev + (size_t)tokens * dims->hidden_size;
-    FFN_CUDA_TRY(cudaMemcpyAsync(x_dev, normed_host, bytes, cudaMemcpyDefault, s), "ffn_forward_mlp_host: input copy");
+    /* Pinned (or registered) host memory is mapped into the device's address space: the kernel reads
+     * its 10 KB of activations and writes its 10 KB of results across PCIe itself, which costs less
+     * than two copy calls.  Pageable memory goes through `staging`. */
+    auto mapped = [](const void *p) -> void * {
+        cudaPointerAttributes attr;
+        if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+        if (attr.type == cudaMemoryTypeUnregistered) return nullptr;
+        return attr.devicePointer; /* device and managed memory: the pointer itself */
+    };
+    uint16_t *x_dev = (uint16_t *)mapped(normed_host), *y_dev = (uint16_t *)mapped(layer_out_host);
+    const bool stage_in = x_dev == nullptr || ((uintptr_t)x_dev & 15), stage_out = y_dev == nullptr;
+    if (stage_in) {
+        x_dev = (uint16_t *)staging;
+        FFN_CUDA_TRY(cudaMemcpyAsync(x_dev, normed_host, bytes, cudaMemcpyDefault, s), "ffn_forward_mlp_host: input copy");
+    }
+    if (stage_out) y_dev = (uint16_t *)staging + (size_t)tokens * dims->hidden_size;
     TpComm *c = (TpComm *)comm;
     const int st = (c && c->tp > 1) ? ffn_forward_mlp_tp(comm, stream, x_dev, ws, y_dev, w, tokens, dims, nullptr)
                                     : ffn_forward_mlp_prepared(nullptr, stream, x_dev, ws, y_dev, w, tokens, dims);
     if (st) return st;
-    FFN_CUDA_TRY(cudaMemcpyAsync(layer_out_host, y_dev, bytes, cudaMemcpyDefault, s), "ffn_forward_mlp_host: output copy");
+    if (stage_out) FFN_CUDA_TRY(cudaMemcpyAsync(layer_out_host, y_dev, bytes, cudaMemcpyDefault, s), "ffn_forward_mlp_host: output copy");
     FFN_CUDA_TRY(cudaStreamSynchronize(s), "ffn_forward_mlp_host: synchronize");
     return FFN_OK;
 }
@@ -357,6 +371,29 @@ int ffn_decode_stack(FfnTpComm *comm, void *stream, void *h, void *ws, void *lay
     const int H = dims->hidden_size, I = dims->intermediate_size;
     if (H <= 0 || I <= 0 || H % FFN_INT4_GROUP || I % FFN_INT4_GROUP)
         return fail(FFN_ERR_CONFIG, "ffn_decode_stack: hidden=%d / intermediate=%d are not whole numbers of %d-wide groups", H, I, FFN_INT4_GROUP);
+    if (tokens <= 2 && num_layers > 0) {
+        /* every layer prepared with ffn_decode_layer_prepare: the whole stack in one persistent launch per 64 layers */
+        bool whole = dims->rms_eps > 0.0f;
+        for (int l = 0; l < num_layers && whole; ++l)
+            whole = layers[l].gate_up_i4 && layers[l].gate_up_i4_scales && layers[l].down_i4 && layers[l].down_i4_scales &&
+                    layers[l].i4_group == FFN_INT4_GROUP && layers[l].post_norm_w;
+        if (whole) {
+            FusedTp t = {};
+            const FusedTp *tp = nullptr;
+            if (c && c->tp > 1) {
+                t.tp = c->tp; t.rank = c->rank; t.peer_slots = c->d_slots;
+                t.slot_stride = c->max_tokens * c->hidden; t.seq = (unsigned *)(c->local + kTpSeqOffset);
+                tp = &t;
+            }
+            unsigned *status = nullptr;
+            int st = fused_status_word(&status);
+            if (st) return st;
+            uint16_t *act = (uint16_t *)ws + (size_t)tokens * H + (size_t)2 * tokens * I;
+            st = kmajor_ffn_launch((cudaStream_t)stream, h, act, layer_out, layers, num_layers, tokens, H, I, tp, h, 1, dims->rms_eps,
+                                   dims->norm_style == 0, status);
+            if (st != FFN_NOT_ADMITTED) return st;
+        }
+    }
     for (int l = 0; l < num_layers; ++l) {
         const int st = decode_layer(c, (cudaStream_t)stream, h, ws, layer_out, layers + l, tokens, dims);
         if (st) return st;

@@ -92,6 +92,10 @@ def _declare(lib):
         "ffn_json_reencode": [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_size_t],
         "ffn_verify_sidecar": [ctypes.c_char_p, ci, ctypes.c_char_p, ctypes.c_size_t],
         "ffn_int4_noalloc_status": [ctypes.POINTER(ci), ctypes.POINTER(ci)],
+        "ffn_decode_layer_prepare": [ctypes.POINTER(MlpWeights), ctypes.POINTER(ModelDims), vp],
+        "ffn_decode_layer_release": [ctypes.POINTER(MlpWeights)],
+        "ffn_decode_layer_is_prepared": [ctypes.POINTER(MlpWeights)],
+        "ffn_int4_describe_kmajor_plan": [ci, ci, ci, ci, ci, ctypes.c_char_p, ctypes.c_size_t],
         "ffn_int4_describe_gemm_plan": [ci, ci, ci, ci, ci, ctypes.c_char_p, ctypes.c_size_t],
         "ffn_forward_mlp_host": [vp, vp, vp, vp, vp, vp, ctypes.POINTER(MlpWeights), ci, ctypes.POINTER(ModelDims)],
         "ffn_tp_allreduce_sum": [vp, vp, vp, ctypes.c_size_t, ci],

@@ -111,6 +111,25 @@ class DenseMlp:
         self.dims.max_chunk = max_chunk
         self.device = gate_up.device
 
+    def prepare(self):
+        """Register the k-major copy of this layer's down projection (include/ffn_int4.h,
+        ffn_decode_layer_prepare): decode calls of 1-2 tokens then take the kernel without the phase
+        barrier, and decode_stack runs in one persistent launch.  Released when the object dies."""
+        check(load().ffn_decode_layer_prepare(ctypes.byref(self.weights), ctypes.byref(self.dims), _stream()))
+        self.prepared = True
+        return self
+
+    def release(self):
+        if getattr(self, "prepared", False):
+            load().ffn_decode_layer_release(ctypes.byref(self.weights))
+            self.prepared = False
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
     def workspace(self, tokens):
         """The reference's layer workspace for the MLP: tokens*(H+3I) bf16 (layers.cu:65)."""
         return torch.empty(tokens * (self.hidden + 3 * self.inter), dtype=torch.bfloat16,

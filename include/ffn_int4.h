@@ -223,6 +223,28 @@ int ffn_forward_mlp_prepared(void *cublas, void *stream, const void *normed, voi
                              void *layer_out, const FfnMlpWeights *w, int tokens,
                              const FfnModelDims *dims);
 
+/* Registers a k-major copy of a layer's down projection, which the decode kernels (1 or 2 tokens)
+ * then use instead of the row-major matrix: WT [I/8][H] 32-bit words (word (kb, h) = the eight codes
+ * k = 8kb..8kb+7 of output row h) and ST [I/128][H] scales, built on `stream` from the device buffers
+ * w->down_i4 / w->down_i4_scales ([H][I/2], [H][I/128]; dims->intermediate_size is the rank-local I).
+ * With it every CTA multiplies the down projection against only the act values it computed itself,
+ * so the kernel needs no grid-wide hand-over between the two projections, and ffn_decode_stack runs
+ * the whole stack in one persistent launch per 64 layers.  Results are not bit-identical to the
+ * row-major kernel's (other summation order; same bars against the oracle).  The copy costs H*I/2 +
+ * H*I/64 bytes of device memory per layer (+33 % of a layer's INT4 bytes) and is found again by the
+ * ADDRESS w->down_i4: ffn_forward_mlp*, ffn_forward_mlp_tp, ffn_forward_mlp_host and ffn_decode_stack
+ * use it whenever the layer they are given has one.  Call again after overwriting the weights, and
+ * ffn_decode_layer_release before freeing them (a stale copy would be used for whatever is put at that
+ * address next).  ffn_load_quantized_ffn[_ranks] registers its layers itself.  Layers without a copy
+ * take the row-major kernel, which reads the reference's own uploads (csrc/engine.cu:2361-2401)
+ * unchanged.  No counterpart in the reference. */
+int ffn_decode_layer_prepare(const FfnMlpWeights *w, const FfnModelDims *dims, void *stream);
+int ffn_decode_layer_release(const FfnMlpWeights *w);
+int ffn_decode_layer_is_prepared(const FfnMlpWeights *w); /* 1 or 0 */
+/* Launch geometry of the kernel over k-major copies, as ffn_int4_describe_plan gives it for the others. */
+int ffn_int4_describe_kmajor_plan(int tokens, int hidden, int intermediate, int sm_count, int smem_optin, char *out,
+                                  size_t out_bytes);
+
 /* The fused FFN (as ffn_forward_mlp_prepared, 1 or 2 tokens) for callers that cannot allocate
  * device memory: a host that handed all of the GPU's memory to its own arena at start-up, so a
  * cudaMalloc from inside a library would fail, or a decode loop that cannot take the device-wide
@@ -318,8 +340,11 @@ unsigned ffn_tp_exchange_tag(unsigned call_number);
  * post_norm_w; `h` is bf16 [tokens][H], updated in place and replicated on every rank; `layer_out`
  * receives the last layer's reduced FFN output; `ws` as for ffn_forward_mlp.  With 1 or 2 tokens a
  * layer is ONE kernel launch (norm, both projections, SiLU*up, cross-rank reduce and residual update
- * fused); with 3..64 tokens it is the norm kernel plus the tensor-core pair.  comm == NULL or a
- * communicator of one rank means TP = 1.  Every rank makes the same call. */
+ * fused); with 3..64 tokens it is the norm kernel plus the tensor-core pair.  When every layer has a
+ * k-major copy (ffn_decode_layer_prepare) and there are 1 or 2 tokens, the whole stack is ONE
+ * persistent launch per 64 layers: the weight stream runs on through the layer boundaries while the
+ * cross-rank exchange and the residual update of the previous layer are in flight.  comm == NULL or
+ * a communicator of one rank means TP = 1.  Every rank makes the same call. */
 int ffn_decode_stack(FfnTpComm *comm, void *stream, void *h, void *ws, void *layer_out,
                      const FfnMlpWeights *layers, int num_layers, int tokens, const FfnModelDims *dims);
 

@@ -11,8 +11,13 @@ one pass with eight tokens serves the one-token case too (token 0).
 
 Stored (BF16 bit patterns):
   tok0_states [L][H]        h after every layer, token 0 (teacher forcing of all layers at M=1)
+  tok0_ffn_out [L][H]       the FFN output y_l of every layer, token 0: the residual stream grows to
+                            |h| ~ 100 over 64 layers (one BF16 ulp of h then exceeds the whole error
+                            budget of y), so the per-layer gate compares y, and checks h = bf16(h + y)
+                            exactly
   m8_layers   [n]           the layers whose input and output states are kept for all eight tokens
   m8_states   [n][2][8][H]  h before and after those layers, tokens 0..7
+  m8_ffn_out  [n][8][H]     their FFN outputs
   final_f64 / final_f32 [8][H]  free-running final state with FP64- / FP32-accumulating matmuls
   spread_rel_l2             relative L2 between the two finals: the oracle-vs-oracle spread that
                             bounds what any implementation with other summation orders can match
@@ -58,6 +63,8 @@ def main():
     h32 = h64.copy()
     tok0 = np.zeros((nl, hidden), np.uint16)
     m8 = np.zeros((len(keep), 2, TOKENS, hidden), np.uint16)
+    tok0_y = np.zeros((nl, hidden), np.uint16)
+    m8_y = np.zeros((len(keep), TOKENS, hidden), np.uint16)
     digest = ""
     t0 = time.time()
     for l in range(nl):
@@ -67,16 +74,19 @@ def main():
                               for a in (lay.gate_up_packed, lay.gate_up_scales, lay.down_packed, lay.down_scales))
         if l in keep:
             m8[keep.index(l), 0] = o.bf16_bits(h64)
-        h64 = o.stack([lay], h64)[0]
+        y64 = o.ffn(lay, o.gemma_rmsnorm(h64, lay.w_norm))
+        h64 = o.residual_add(h64, y64)
         h32 = o.stack([lay], h32, accumulate="f32")[0]
         tok0[l] = o.bf16_bits(h64[0])
+        tok0_y[l] = o.bf16_bits(y64[0])
         if l in keep:
             m8[keep.index(l), 1] = o.bf16_bits(h64)
+            m8_y[keep.index(l)] = o.bf16_bits(y64)
         print(f"layer {l}: {time.time() - t0:.0f} s, |h| rms {np.sqrt((h64 ** 2).mean()):.3f}, "
               f"f32-vs-f64 rel-L2 so far {o.compare(h32, h64)[1]:.3g}", flush=True)
     spread = o.compare(h32, h64)[1]
     spread0 = o.compare(h32[:1], h64[:1])[1]
-    np.savez_compressed(args.out, tok0_states=tok0, m8_layers=np.array(keep), m8_states=m8,
+    np.savez_compressed(args.out, tok0_states=tok0, tok0_ffn_out=tok0_y, m8_layers=np.array(keep), m8_states=m8, m8_ffn_out=m8_y,
                         final_f64=o.bf16_bits(h64), final_f32=o.bf16_bits(h32), spread_rel_l2=np.float64(spread),
                         spread_rel_l2_token0=np.float64(spread0), digest_layer0=np.array(digest),
                         shape=np.array([nl, hidden, inter, TOKENS, SEED]))

@@ -30,13 +30,16 @@ def host_f32(t_bf16):
     return t_bf16.detach().float().cpu().numpy()
 
 
-def upload_layer(layer, device, tp=1, rank=0, with_norm=False):
+def upload_layer(layer, device, tp=1, rank=0, with_norm=False, prepare=False):
+    """``prepare``: also register the k-major copy of the down projection, so that calls of one or two
+    tokens take the kernel without the phase barrier (ffn_decode_layer_prepare)."""
     from haskell_infer_demo_b200.ops import DenseMlp
     gp, gs, dp, ds = o.slice_rank(layer.gate_up_packed, layer.gate_up_scales, layer.down_packed,
                                   layer.down_scales, tp, rank)
     norm = dev_bf16(layer.w_norm, device) if (with_norm and layer.w_norm is not None) else None
-    return DenseMlp(dev_u8(gp, device), dev_bits(gs, device), dev_u8(dp, device), dev_bits(ds, device),
-                    post_norm_w=norm)
+    mlp = DenseMlp(dev_u8(gp, device), dev_bits(gs, device), dev_u8(dp, device), dev_bits(ds, device),
+                   post_norm_w=norm)
+    return mlp.prepare() if prepare else mlp
 
 
 def bf16_ulp(values):

@@ -79,9 +79,10 @@ def _cached_layer(hidden, inter, row):
 
 
 @pytest.mark.parametrize("hidden,inter", [(1024, 3072), (5120, 17408)])
-@pytest.mark.parametrize("tokens", [1, 2, 8, 16])
-def test_ffn_second_projection_is_exact_on_a_one_hot_act(cuda, hidden, inter, tokens):
-    """The whole FFN call (single-launch kernel for 1-2 tokens, tensor-core pair for 8 and 16) on a
+@pytest.mark.parametrize("tokens,kmajor", [(1, False), (2, False), (8, False), (16, False), (1, True), (2, True)])
+def test_ffn_second_projection_is_exact_on_a_one_hot_act(cuda, hidden, inter, tokens, kmajor):
+    """The whole FFN call (single-launch kernel for 1-2 tokens - row-major, or over the k-major copy of
+    the down projection - and the tensor-core pair for 8 and 16) on a
     layer whose act has ONE non-zero element: y must equal bf16(dequantized down column * act) bit for
     bit, act being the value the device itself left in the workspace (SiLU uses the device's __expf,
     and the first projection rounds its sums, so act is only checked to be near the CPU chain's and
@@ -90,7 +91,7 @@ def test_ffn_second_projection_is_exact_on_a_one_hot_act(cuda, hidden, inter, to
     layer, deq_down = _cached_layer(hidden, inter, live[0])
     rng = np.random.default_rng(tokens)
     x = o.bf16_round(rng.standard_normal((tokens, hidden), dtype=np.float32))
-    mlp = upload_layer(layer, cuda)
+    mlp = upload_layer(layer, cuda, prepare=kmajor)
     ws = mlp.workspace(tokens)
     y = mlp.forward_mlp_prepared(dev_bf16(x, cuda), ws=ws)
     L.device_status()
@@ -106,14 +107,14 @@ def test_ffn_second_projection_is_exact_on_a_one_hot_act(cuda, hidden, inter, to
     assert same.all(), f"H={hidden} I={inter} M={tokens}: {np.count_nonzero(~same)} outputs differ"
 
 
-@pytest.mark.parametrize("tokens", [1, 2, 8])
-def test_ffn_first_projection_is_exact_on_a_one_hot_input(cuda, tokens):
+@pytest.mark.parametrize("tokens,kmajor", [(1, False), (2, False), (8, False), (1, True), (2, True)])
+def test_ffn_first_projection_is_exact_on_a_one_hot_input(cuda, tokens, kmajor):
     """One-hot x: gate and up are single products, so act may differ from the CPU chain only through
     __expf (at most one BF16 ulp, and on few elements)."""
     hidden, inter = 1024, 3072
     _, layers = o.draw_config(hidden, inter, 17, tokens=tokens)
     layer = layers[0]
-    mlp = upload_layer(layer, cuda)
+    mlp = upload_layer(layer, cuda, prepare=kmajor)
     ws = mlp.workspace(tokens)
     for step in range(8):
         x = np.zeros((tokens, hidden), np.float32)

@@ -45,13 +45,13 @@ def test_tp_parity_multi_gpu(ranks):
     assert proc.returncode == 0 and "tp_worker ok" in proc.stdout, proc.stdout[-3000:] + proc.stderr[-3000:]
 
 
-@pytest.mark.parametrize("tokens", [1, 8])
-def test_withheld_rank_is_reported_not_waited_for_forever(cuda, tokens):
+@pytest.mark.parametrize("tokens,kmajor", [(1, False), (8, False), (1, True), (2, True)])
+def test_withheld_rank_is_reported_not_waited_for_forever(cuda, tokens, kmajor):
     """Failure detection without a GPU fault: rank 0 of a two-rank communicator runs alone (rank 1 is
     never launched, so its partial sums never arrive).  The kernel's wait for them is bounded (about
     a second); it must return, the host must see the status naming the wait, and the device must
-    stay usable: the next plain call gives the right answer.  Covers the single-pass kernel and the
-    batched pair."""
+    stay usable: the next plain call gives the right answer.  Covers the row-major single-pass kernel,
+    the batched pair and the kernel over k-major copies."""
     from oracle import ffn_oracle as o
     from gpu_util import assert_ffn_close, dev_bf16, host_f32, upload_layer
     from haskell_infer_demo_b200 import lib as L
@@ -59,12 +59,12 @@ def test_withheld_rank_is_reported_not_waited_for_forever(cuda, tokens):
     x, layers = o.draw_config(1024, 3072, 0, tokens=tokens)
     comms = TpComm.local([cuda, cuda], 1024, 8)      # both ends on this device; only rank 0 is driven
     try:
-        half = upload_layer(layers[0], cuda, tp=2, rank=0)
+        half = upload_layer(layers[0], cuda, tp=2, rank=0, prepare=kmajor)
         comms[0].forward_mlp(half, dev_bf16(x, cuda))
         with pytest.raises(L.FfnError, match="partial sums"):
             L.device_status()
         L.device_status()                            # the status was cleared by reading it
-        whole = upload_layer(layers[0], cuda)
+        whole = upload_layer(layers[0], cuda, prepare=kmajor)
         got = host_f32(whole.forward_mlp_prepared(dev_bf16(x, cuda)))
         L.device_status()
         assert_ffn_close(got, o.ffn(layers[0], x), "after a withheld rank")
@@ -101,7 +101,11 @@ def test_one_process_drives_every_rank_like_the_reference(cuda):
         comms = TpComm.local(devices, hidden, 16)
         try:
             mlps = [upload_layer(layers[0], d, tp=ranks, rank=r) for r, d in enumerate(devices)]
-            for tokens in (1, 2, 16):
+            for tokens, kmajor in ((1, False), (2, False), (16, False), (1, True), (2, True)):
+                if kmajor:                                            # over the k-major copies of the down slices
+                    for r, d in enumerate(devices):
+                        with torch.cuda.device(d):
+                            mlps[r].prepare()
                 x = xs[:tokens]
                 want = o.ffn(layers[0], x)
                 xd = [dev_bf16(x, d) for d in devices]
@@ -115,7 +119,7 @@ def test_one_process_drives_every_rank_like_the_reference(cuda):
                     for d in devices:
                         with torch.cuda.device(d):
                             L.device_status()
-                    assert_ffn_close(host_f32(outs[0]), want, f"one process, {ranks} ranks, H={hidden} M={tokens}")
+                    assert_ffn_close(host_f32(outs[0]), want, f"one process, {ranks} ranks, H={hidden} M={tokens} k-major={kmajor}")
                     for r in range(1, ranks):
                         assert torch.equal(outs[r].cpu().view(torch.int16), outs[0].cpu().view(torch.int16)), f"rank {r} differs"
         finally:
