@@ -538,6 +538,11 @@ struct QuantizedFfn {
         int restore = 0;
         (void)cudaGetDevice(&restore);
         (void)cudaSetDevice(device);
+        for (const LoadedLayer &l : layer) { /* the k-major copies registered for these addresses go first */
+            FfnMlpWeights w = {};
+            w.down_i4 = l.down;
+            if (l.down) (void)ffn_decode_layer_release(&w);
+        }
         for (void *p : owned) cudaFree(p);
         (void)cudaSetDevice(restore);
     }
@@ -792,6 +797,28 @@ int ffn_shard_view(int rule, long long rows, long long cols, int tp, int rank, l
     return shard_view(rule, rows, cols, tp, rank, view4);
 }
 
+/* Registers the k-major copy of every loaded layer's down projection (the decode kernels of one and
+ * two tokens use it, see ffn_decode_layer_prepare).  All or nothing, like the load itself. */
+static int prepare_loaded(QuantizedFfn *q) {
+    int restore = 0;
+    (void)cudaGetDevice(&restore);
+    int st = FFN_OK;
+    if (cudaSetDevice(q->device) != cudaSuccess) st = fail(FFN_ERR_CUDA, "ffn_load_quantized_ffn: cannot select device %d", q->device);
+    FfnModelDims dims = {};
+    dims.hidden_size = q->hidden;
+    dims.intermediate_size = q->inter_local;
+    for (int l = 0; l < q->layers && st == FFN_OK; ++l) {
+        FfnMlpWeights w = {};
+        w.down_i4 = q->layer[l].down;
+        w.down_i4_scales = q->layer[l].down_scales;
+        w.i4_group = FFN_INT4_GROUP;
+        st = ffn_decode_layer_prepare(&w, &dims, nullptr);
+    }
+    if (st == FFN_OK && cudaDeviceSynchronize() != cudaSuccess) st = fail(FFN_ERR_CUDA, "ffn_load_quantized_ffn: building the k-major copies failed");
+    (void)cudaSetDevice(restore);
+    return st;
+}
+
 int ffn_load_quantized_ffn(const char *manifest_dir, int num_layers, int hidden, int intermediate, int tp, int rank,
                            FfnQuantizedFfn **out) {
     clear_error();
@@ -799,7 +826,8 @@ int ffn_load_quantized_ffn(const char *manifest_dir, int num_layers, int hidden,
     int dev = 0;
     FFN_CUDA_TRY(cudaGetDevice(&dev), "ffn_load_quantized_ffn: no CUDA device");
     QuantizedFfn *q = nullptr;
-    const int st = load_ranks(manifest_dir, num_layers, hidden, intermediate, tp < 1 ? 1 : tp, &rank, &dev, 1, &q);
+    int st = load_ranks(manifest_dir, num_layers, hidden, intermediate, tp < 1 ? 1 : tp, &rank, &dev, 1, &q);
+    if (st == FFN_OK && (st = prepare_loaded(q)) != FFN_OK) { delete q; q = nullptr; }
     if (st == FFN_OK) *out = (FfnQuantizedFfn *)q;
     return st;
 }
@@ -811,9 +839,13 @@ int ffn_load_quantized_ffn_ranks(const char *manifest_dir, int num_layers, int h
     int ranks[16];
     QuantizedFfn *q[16] = {};
     for (int i = 0; i < tp; ++i) ranks[i] = i;
-    const int st = load_ranks(manifest_dir, num_layers, hidden, intermediate, tp, ranks, devices, tp, q);
-    if (st == FFN_OK)
-        for (int i = 0; i < tp; ++i) out[i] = (FfnQuantizedFfn *)q[i];
+    int st = load_ranks(manifest_dir, num_layers, hidden, intermediate, tp, ranks, devices, tp, q);
+    for (int i = 0; i < tp && st == FFN_OK; ++i) st = prepare_loaded(q[i]);
+    if (st != FFN_OK) {
+        for (int i = 0; i < tp; ++i) delete q[i];
+        return st;
+    }
+    for (int i = 0; i < tp; ++i) out[i] = (FfnQuantizedFfn *)q[i];
     return st;
 }
 

@@ -134,8 +134,15 @@ def test_kmajor_more_layers_than_one_launch_takes(cuda):
         decode_stack([m], h2)
     L.device_status()
     assert torch.equal(h2.view(torch.int16), h.view(torch.int16))
-    ref32 = o.stack(layers, h0, accumulate="f32")
-    assert o.compare(host_f32(h), ref[-1])[1] <= max(5e-3, 2 * o.compare(ref32[-1], ref[-1])[1])
+    # 70 free-running layers of a narrow model are chaotic under BF16 rounding (one rounding that falls
+    # differently decorrelates the stream), so this is a sanity bound; the per-layer bars are held by the
+    # teacher-forced tests, and the launches' equality with the layer-by-layer run is exact above
+    assert o.compare(host_f32(h), ref[-1])[1] <= 3e-2
+    for l in (0, 63, 64, 69):                                 # either side of the launch boundary
+        hl = dev_bf16(h0 if l == 0 else ref[l - 1], cuda).clone()
+        decode_stack([mlps[l]], hl)
+        L.device_status()
+        assert_ffn_close(host_f32(hl), ref[l], f"layer {l} of 70 teacher-forced")
 
 
 def test_kmajor_residual_and_norm_variants(cuda):

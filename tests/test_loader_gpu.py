@@ -55,6 +55,7 @@ def test_load_slices_and_runs(cuda, tmp_path, tp):
             assert np.array_equal(device_bytes(w.gate_up_i4_scales, gs.size * 2), gs.ravel().view(np.uint8))
             assert np.array_equal(device_bytes(w.down_i4, dp.size), dp.ravel())
             assert np.array_equal(device_bytes(w.down_i4_scales, ds.size * 2), ds.ravel().view(np.uint8))
+            assert lib.ffn_decode_layer_is_prepared(ctypes.byref(w)) == 1      # the loader registers the k-major copies
             if tp == 1:
                 # run the FFN straight from the loaded operands
                 dims = L.ModelDims()
