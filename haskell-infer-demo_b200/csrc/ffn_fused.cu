@@ -519,6 +519,7 @@ static DeviceState g_dev[64];
 static long long *g_trace = nullptr; /* debugging aid: device buffer for CTA 0's clock stamps */
 
 void fused_set_trace(long long *device_buffer) { g_trace = device_buffer; }
+long long *fused_get_trace() { return g_trace; }
 static std::mutex g_dev_mutex;
 
 static int device_state(DeviceState **out) {

@@ -92,10 +92,14 @@ struct KmSmem {
     uint64_t part_empty[kPartSlots];
     uint64_t x_ready;         /* the layer's input is staged in shared memory (loader warps arrive) */
     uint64_t act_ready;       /* this CTA's act values and their byte planes are in place (epilogue arrives) */
+    uint64_t p_open;          /* every CTA has stored this layer's partial sums (the epilogue warp saw the counter) */
+    uint64_t h_open;          /* every CTA has published this layer's residual rows (likewise) */
+    unsigned arrive_p, arrive_h; /* consumer warps of this CTA that finished storing / publishing (monotonic) */
     int abort_flag;
     unsigned base;            /* the arrival counters' value when the launch began */
     unsigned epoch;           /* layers this device has run before this launch: layer l's words carry km_tag(epoch + l) */
     unsigned seq0;            /* the communicator's call number when the launch began */
+    int pad[2];
     float norm_red[2][kConsumerWarps + 3];
     float fac[2][kKmMaxSeg + 1];
     __align__(16) uint32_t planes[2][kKmMaxKb][4];   /* [token][k-block]{he, ho, le, lo} */
@@ -111,8 +115,13 @@ __device__ __forceinline__ void km_give_up(KmSmem *sm, unsigned *status, int whe
     sm->abort_flag = 1;
     atomicCAS(status, 0u, (unsigned)where | ((unsigned)blockIdx.x << 8));
 }
+/* Optional timeline: 16 stamps per CTA of the global nanosecond timer (comparable across SMs). */
 __device__ __forceinline__ void km_stamp(const KmParams &P, int slot) {
-    if (P.trace && blockIdx.x == 0) P.trace[slot] = clock64();
+    if (P.trace) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        P.trace[(size_t)blockIdx.x * 16 + slot] = (long long)t;
+    }
 }
 /* first k-block of CTA `cta` (total * ctas < 2^32 is checked on the host) */
 __device__ __forceinline__ int km_begin(int total, int cta, int ctas) {
@@ -134,13 +143,17 @@ __device__ __forceinline__ void km_store2(unsigned long long *p, unsigned long l
 __device__ __forceinline__ void km_store1(unsigned long long *p, unsigned long long a) {
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
 }
+/* Loads of tagged words come in batches (up to 20 per lane) whose results are all checked afterwards,
+ * so they must overlap: plain loads served by the L2 (.cg: no L1 allocation, so a repeated poll reads
+ * the L2 again).  Loads qualified .relaxed.gpu measured one L2 round trip EACH, back to back - 6 us for
+ * a batch.  A word is only ever accepted on its tag, so a stale answer costs a retry, never an error. */
 __device__ __forceinline__ unsigned long long km_load1(const unsigned long long *p) {
     unsigned long long w;
-    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    asm volatile("ld.global.cg.u64 %0, [%1];" : "=l"(w) : "l"(p));
     return w;
 }
 __device__ __forceinline__ void km_load2(const unsigned long long *p, unsigned long long &a, unsigned long long &b) {
-    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+    asm volatile("ld.global.cg.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p));
 }
 __device__ __forceinline__ unsigned km_load_counter(const unsigned *p) {
     unsigned v;
@@ -234,13 +247,27 @@ __device__ __forceinline__ void km_producer(const KmParams &P, KmSmem *sm, uint8
 
 /* ---- epilogue warp: phase-1 sums -> act, then the byte planes of this CTA's act values --------- */
 template <int MT>
-__device__ __forceinline__ bool km_epilogue_layer(const KmParams &P, KmSmem *sm, int l, int kb0, int kb1, int part_tile0) {
+__device__ __forceinline__ bool km_epilogue_layer(const KmParams &P, KmSmem *sm, int l, int kb0, int kb1, int part_tile0, unsigned &base) {
     constexpr int NVROW = 2 * MT;
     const PhasePlan &pl = P.p1;
     const int lane = threadIdx.x & 31;
     const int pair0 = kb0 * 8, pair1 = kb1 * 8;
     const int ntiles = (pair1 - pair0 + pl.TR - 1) / pl.TR;
-    if (kb1 == kb0) return true; /* a CTA without k-blocks has no act: its consumers do not wait for any */
+    if (l == 0) {
+        /* Both arrival counters stood at `base` when the launch began; `epoch` numbers the layers this
+         * device has run (the tags); seq0 is the communicator's call number.  Stable until CTA 0 rewrites
+         * them at its exit, which it reaches only after every CTA has arrived at the last layer's
+         * counters.  Read here, off everybody's critical path, and published to the consumers by this
+         * warp's arrivals at act_ready / p_open. */
+        unsigned b = 0;
+        if (lane == 0) {
+            b = P.sync[2];
+            sm->base = b;
+            sm->epoch = P.sync[3];
+            sm->seq0 = P.tp > 1 ? ld_acquire_gpu(P.tp_seq) : 0u;
+        }
+        base = __shfl_sync(0xffffffffu, b, 0);
+    }
     for (int lt = 0; lt < ntiles; ++lt) {
         const int pt = part_tile0 + lt;
         const int pslot = pt % kPartSlots;
@@ -297,11 +324,29 @@ __device__ __forceinline__ bool km_epilogue_layer(const KmParams &P, KmSmem *sm,
         }
     }
     __syncwarp();
-    if (lane == 0) {
+    if (lane == 0 && kb1 > kb0) { /* a CTA without k-blocks has no act: its consumers do not wait for any */
         mbar_arrive(&sm->act_ready);
         if (l == 0) km_stamp(P, 5);
     }
-    return true;
+    /* From here on this warp is idle until the next layer, so it watches the two arrival counters for
+     * the whole CTA (one poller per SM): when every CTA has stored its partial sums the reducers may
+     * start reading them, when every CTA has published its rows of h the loaders may.  Hints only -
+     * the words validate themselves. */
+    bool ok = true;
+    if (lane == 0) {
+        const unsigned target = base + (unsigned)(l + 1) * gridDim.x;
+        ok = km_wait_counter(P.sync + 0, target, &sm->abort_flag);
+        if (ok) {
+            mbar_arrive(&sm->p_open);
+            if (l == 0) km_stamp(P, 13);
+            if (l + 1 < P.L) {
+                ok = km_wait_counter(P.sync + 1, target, &sm->abort_flag);
+                if (ok) mbar_arrive(&sm->h_open);
+            }
+        }
+        if (!ok) km_give_up(sm, P.status, ST_PARTIALS);
+    }
+    return __shfl_sync(0xffffffffu, ok, 0);
 }
 
 /* ---- consumers: staging of the layer's input ---------------------------------------------------- */
@@ -309,18 +354,77 @@ __device__ __forceinline__ bool km_epilogue_layer(const KmParams &P, KmSmem *sm,
  * bring the layer's input into shared memory - from the caller's buffer for the first layer, from the
  * tagged words the previous layer's owners published for the others - and leave the sums of squares
  * for the fused RMSNorm.  Returns false when a wait ran out. */
+/* The first layer's input is in place when the kernel starts: the loader threads fetch their slices
+ * before anything else happens (before the producer has filled the memory system with bulk copies,
+ * behind which a load issued later would queue for microseconds). */
 template <int CIT, int MT>
-__device__ __forceinline__ bool km_stage_input(const KmParams &P, KmSmem *sm, uint16_t *xs, int l, unsigned base) {
+__device__ __forceinline__ void km_prefetch_input(const KmParams &P, uint32_t (&pre)[CIT][MT][16]) {
+    const PhasePlan &pl = P.p1;
+    const int ti = threadIdx.x - 32;
+#pragma unroll
+    for (int c = 0; c < CIT; ++c)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const int col = ti + c * pl.CT;
+            const bool on = ti >= 0 && ti < pl.CT && col < pl.cpr;
+            const uint16_t *src = P.x + (size_t)m * pl.K + (size_t)(on ? col : 0) * 32;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 t4 = make_uint4(0, 0, 0, 0);
+                if (on) t4 = __ldg((const uint4 *)(src + q * 8));
+                pre[c][m][4 * q] = t4.x; pre[c][m][4 * q + 1] = t4.y; pre[c][m][4 * q + 2] = t4.z; pre[c][m][4 * q + 3] = t4.w;
+            }
+        }
+}
+
+/* ... and put them into shared memory as soon as the barriers exist, with the sums of squares for a
+ * fused RMSNorm, exactly as km_stage_input does for the later layers. */
+template <int CIT, int MT>
+__device__ __forceinline__ void km_stage_first(const KmParams &P, KmSmem *sm, uint16_t *xs, const uint32_t (&pre)[CIT][MT][16]) {
+    const PhasePlan &pl = P.p1;
+    const int ti = threadIdx.x - 32, lane = threadIdx.x & 31, wp = ti >> 5;
+    if (ti < 0 || wp >= (pl.CT + 31) / 32) return;
+    float ss[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) ss[m] = 0.0f;
+#pragma unroll
+    for (int c = 0; c < CIT; ++c) {
+        const int col = ti + c * pl.CT;
+        if (ti >= pl.CT || col >= pl.cpr) continue;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            uint32_t *dst = (uint32_t *)(xs + (size_t)m * pl.K + (size_t)col * 32);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                *(uint4 *)(dst + 4 * q) = make_uint4(pre[c][m][4 * q], pre[c][m][4 * q + 1], pre[c][m][4 * q + 2], pre[c][m][4 * q + 3]);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+                ss[m] = fmaf(bf16_lo(pre[c][m][q]), bf16_lo(pre[c][m][q]), ss[m]);
+                ss[m] = fmaf(bf16_hi(pre[c][m][q]), bf16_hi(pre[c][m][q]), ss[m]);
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        const float tot = warp_sum(ss[m]);
+        if (lane == 0) sm->norm_red[m][wp] = tot;
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sm->x_ready);
+}
+
+template <int CIT, int MT>
+__device__ __forceinline__ bool km_stage_input(const KmParams &P, KmSmem *sm, uint16_t *xs, int l) {
+    if (l == 0) return true; /* staged by km_stage_first */
     const PhasePlan &pl = P.p1;
     const int ti = threadIdx.x - 32, lane = threadIdx.x & 31, wp = ti >> 5;
     const int loader_warps = (pl.CT + 31) / 32;
     if (wp >= loader_warps) return true;
     const bool loader = ti < pl.CT;
-    if (l > 0) { /* hint: every CTA's owners have published the previous layer's h */
-        bool ok = true;
-        if (lane == 0) ok = km_wait_counter(P.sync + 1, base + (unsigned)l * (unsigned)(kConsumerWarps * gridDim.x), &sm->abort_flag);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) { if (lane == 0) km_give_up(sm, P.status, ST_NEXT_X); return false; }
+    if (!mbar_wait<64>(&sm->h_open, (uint32_t)(l - 1) & 1u, &sm->abort_flag)) {
+        /* (the epilogue warp watches the arrival counter for the whole CTA: one poller per SM) */
+        if (lane == 0) km_give_up(sm, P.status, ST_NEXT_X);
+        return false;
     }
     const unsigned tag = km_tag(sm->epoch + (unsigned)l - 1u); /* the previous layer's */
     float ss[MT];
@@ -334,14 +438,7 @@ __device__ __forceinline__ bool km_stage_input(const KmParams &P, KmSmem *sm, ui
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             uint32_t v[16];
-            if (l == 0) {
-                const uint16_t *src = P.x + (size_t)m * pl.K + (size_t)col * 32;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint4 t4 = __ldg((const uint4 *)(src + q * 8));
-                    v[4 * q] = t4.x; v[4 * q + 1] = t4.y; v[4 * q + 2] = t4.z; v[4 * q + 3] = t4.w;
-                }
-            } else {
+            {
                 const unsigned long long *src = P.hx + (size_t)m * pl.K + (size_t)col * 32;
                 bool in = false;
                 for (uint32_t k = 0; k < kTpPollLimit && !in; ++k) {
@@ -384,8 +481,7 @@ __device__ __forceinline__ bool km_stage_input(const KmParams &P, KmSmem *sm, ui
 /* ---- consumers: one layer ----------------------------------------------------------------------- */
 template <int CIT, int MT>
 __device__ __forceinline__ bool km_consumer_layer(const KmParams &P, KmSmem *sm, uint16_t *xs, uint8_t *ring, int l,
-                                                  int kb0, int kb1, int ring_tile0, int part_tile0, unsigned base,
-                                                  unsigned tp_seq0) {
+                                                  int kb0, int kb1, int ring_tile0, int part_tile0) {
     constexpr int NVROW = 2 * MT;
     constexpr int VALS = 4 * MT;      /* values a thread carries through a phase-1 tile */
     constexpr int JTM = VALS / NVROW; /* = 2 row steps per thread per tile */
@@ -404,8 +500,7 @@ __device__ __forceinline__ bool km_consumer_layer(const KmParams &P, KmSmem *sm,
     const int nt2 = (nkb + P.R2 - 1) / P.R2;
 
     /* ---------------- the layer's input: staged by the loader threads, prepared by everyone ------- */
-    if (!km_stage_input<CIT, MT>(P, sm, xs, l, base)) return false;
-    const unsigned epoch = sm->epoch;
+    if (!km_stage_input<CIT, MT>(P, sm, xs, l)) return false;
     if (!mbar_wait<32>(&sm->x_ready, (uint32_t)l & 1u, &sm->abort_flag)) {
         km_give_up(sm, P.status, ST_NEXT_X);
         return false;
@@ -528,8 +623,10 @@ __device__ __forceinline__ bool km_consumer_layer(const KmParams &P, KmSmem *sm,
     if (threadIdx.x == 32 && l == 0) km_stamp(P, 6);
     const int H = P.H;
     const int npairs = (H / 2 + kConsumerThreads - 1) / kConsumerThreads; /* <= kKmMaxPairs, checked on the host */
-    const unsigned tag = km_tag(epoch + (unsigned)l);
     if (nkb > 0) {
+        /* (the launch's layer count and call number were read by the epilogue warp and are published
+         * by its arrivals at act_ready / p_open) */
+        const unsigned tag = km_tag(sm->epoch + (unsigned)l);
         int acc[MT][2 * kKmMaxPairs];
         float y[MT][2 * kKmMaxPairs];
         uint32_t sc[kKmMaxPairs];
@@ -617,7 +714,7 @@ __device__ __forceinline__ bool km_consumer_layer(const KmParams &P, KmSmem *sm,
         }
     }
     __syncwarp();
-    if (lane == 0) km_arrive_counter(P.sync + 0);
+    if (lane == 0 && atomicAdd(&sm->arrive_p, 1u) % kConsumerWarps == kConsumerWarps - 1) km_arrive_counter(P.sync + 0); /* the CTA's last warp */
     if (threadIdx.x == 32 && l == 0) km_stamp(P, 8);
 
     /* ---------------- the rows this CTA owns: sum over CTAs, cross-rank exchange, output ----------- */
@@ -626,12 +723,13 @@ __device__ __forceinline__ bool km_consumer_layer(const KmParams &P, KmSmem *sm,
      * same bits in every lane), so the result does not depend on timing.  Under tensor parallelism
      * lane s then sends the rank's sum to ranks s (and s+8), waits for rank s's (and s+8's) word in
      * this rank's own buffer, and the values are added in rank order. */
-    {
-        bool ok = true;
-        if (lane == 0) ok = km_wait_counter(P.sync + 0, base + (unsigned)(l + 1) * (unsigned)(kConsumerWarps * G), &sm->abort_flag);
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) { if (lane == 0) km_give_up(sm, P.status, ST_PARTIALS); return false; }
+    if (!mbar_wait<64>(&sm->p_open, (uint32_t)l & 1u, &sm->abort_flag)) {
+        if (lane == 0) km_give_up(sm, P.status, ST_PARTIALS);
+        return false;
     }
+    if (threadIdx.x == 32 && l == 0) km_stamp(P, 10);
+    const unsigned tag = km_tag(sm->epoch + (unsigned)l);
+    const unsigned tp_seq0 = sm->seq0;
     const int b2 = km_begin(H, blockIdx.x, G), e2 = km_begin(H, blockIdx.x + 1, G);
     const int nitems = (e2 - b2) * MT;
     const int s8 = lane & 7, grp8 = ti >> 3;
@@ -639,10 +737,17 @@ __device__ __forceinline__ bool km_consumer_layer(const KmParams &P, KmSmem *sm,
     const unsigned gmask = 0xFFu << (lane & 24);
     const int KB = P.I / 8;
     const unsigned seq = tp_seq0 + (unsigned)l;
-    unsigned use_mask = 0; /* bit i: CTA s8 + 8i exists and owns k-blocks (a CTA without any stores nothing) */
-    for (int i = 0; i < kKmMaxQ; ++i) {
-        const int q = s8 + 8 * i;
-        if (q < G && km_begin(KB, q + 1, G) > km_begin(KB, q, G)) use_mask |= 1u << i;
+    /* bit i: CTA s8 + 8i exists and owns k-blocks (a CTA without any stores nothing).  With at least as
+     * many k-blocks as CTAs every CTA owns some, and no division is needed to know it. */
+    unsigned use_mask = 0;
+    if (KB >= G) {
+        for (int i = 0; i < kKmMaxQ; ++i)
+            if (s8 + 8 * i < G) use_mask |= 1u << i;
+    } else {
+        for (int i = 0; i < kKmMaxQ; ++i) {
+            const int q = s8 + 8 * i;
+            if (q < G && km_begin(KB, q + 1, G) > km_begin(KB, q, G)) use_mask |= 1u << i;
+        }
     }
     bool failed = false;
     for (int it0 = 0; it0 < nitems; it0 += kGroups) { /* uniform trip count over the CTA */
@@ -653,8 +758,10 @@ __device__ __forceinline__ bool km_consumer_layer(const KmParams &P, KmSmem *sm,
         /* the words of this lane: all loads first, then the tag checks, so the loads overlap */
         unsigned long long w[kKmMaxQ];
         bool in = false;
+        uint32_t attempts = 0;
         for (uint32_t k = 0; k < kTpPollLimit && !in; ++k) {
             in = true;
+            ++attempts;
 #pragma unroll
             for (int i = 0; i < kKmMaxQ; ++i) {
                 w[i] = (unsigned long long)tag << 32; /* value 0.0, tag of this layer */
@@ -667,6 +774,7 @@ __device__ __forceinline__ bool km_consumer_layer(const KmParams &P, KmSmem *sm,
                 __nanosleep(32);
             }
         }
+        if (threadIdx.x == 32 && l == 0 && it0 == 0) { km_stamp(P, 11); if (P.trace) P.trace[(size_t)blockIdx.x * 16 + 14] = (long long)attempts; }
         float a = 0.0f;
 #pragma unroll
         for (int i = 0; i < kKmMaxQ; ++i) a += __uint_as_float((unsigned)w[i]);
@@ -717,7 +825,7 @@ __device__ __forceinline__ bool km_consumer_layer(const KmParams &P, KmSmem *sm,
         }
     }
     __syncwarp();
-    if (lane == 0) km_arrive_counter(P.sync + 1);
+    if (lane == 0 && atomicAdd(&sm->arrive_h, 1u) % kConsumerWarps == kConsumerWarps - 1) km_arrive_counter(P.sync + 1);
     if (threadIdx.x == 32 && l == 0) km_stamp(P, 9);
     return !failed;
 }
@@ -737,19 +845,20 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_kmajor_kernel(const __grid_co
         if (lane >= 8 && lane < 8 + kPartSlots) { mbar_init(&sm->part_full[lane - 8], kConsumerWarps); mbar_init(&sm->part_empty[lane - 8], 1); }
         if (lane == 16) mbar_init(&sm->x_ready, (P.p1.CT + 31) / 32);
         if (lane == 17) mbar_init(&sm->act_ready, 1);
-        if (lane == 30) {
-            /* both arrival counters stood at `base` when the launch began; `epoch` numbers the layers this
-             * device has run (the tags).  Stable until CTA 0 rewrites them at its exit, which it reaches
-             * only after every CTA has arrived at the last layer's counters. */
-            sm->base = P.sync[2];
-            sm->epoch = P.sync[3];
-            sm->seq0 = P.tp > 1 ? ld_acquire_gpu(P.tp_seq) : 0u;
-        }
+        if (lane == 18) mbar_init(&sm->p_open, 1);
+        if (lane == 19) mbar_init(&sm->h_open, 1);
+        if (lane == 20) { sm->arrive_p = 0; sm->arrive_h = 0; }
         if (lane == 31) sm->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        __syncwarp();
+        /* the barriers exist: this warp (the producer) goes on at once, the others wait for it here */
+        asm volatile("bar.arrive 1, %0;" ::"n"(kThreads) : "memory");
+    } else {
+        uint32_t pre[CIT][MT][16];
+        km_prefetch_input<CIT, MT>(P, pre); /* in flight while warp 0 sets the barriers up */
+        asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+        km_stage_first<CIT, MT>(P, sm, xs, pre);
     }
-    __syncthreads();
-    const unsigned base = sm->base, seq0 = sm->seq0;
     const int G = (int)gridDim.x, KB = P.I / 8;
     const int kb0 = km_begin(KB, blockIdx.x, G), kb1 = km_begin(KB, blockIdx.x + 1, G);
     const int nt1 = ((kb1 - kb0) * 8 + P.p1.TR - 1) / P.p1.TR;
@@ -762,14 +871,15 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_kmajor_kernel(const __grid_co
         }
     } else if (warp <= kConsumerWarps) {
         for (int l = 0; l < P.L; ++l)
-            if (!km_consumer_layer<CIT, MT>(P, sm, xs, ring, l, kb0, kb1, l * (nt1 + nt2), l * nt1, base, seq0)) break;
+            if (!km_consumer_layer<CIT, MT>(P, sm, xs, ring, l, kb0, kb1, l * (nt1 + nt2), l * nt1)) break;
     } else {
+        unsigned base = 0;
         for (int l = 0; l < P.L; ++l)
-            if (!km_epilogue_layer<MT>(P, sm, l, kb0, kb1, l * nt1)) break;
+            if (!km_epilogue_layer<MT>(P, sm, l, kb0, kb1, l * nt1, base)) break;
     }
     __syncthreads();
     if (blockIdx.x == 0 && threadIdx.x == 0 && !sm->abort_flag) {
-        P.sync[2] = base + (unsigned)P.L * (unsigned)(kConsumerWarps * G);
+        P.sync[2] = sm->base + (unsigned)P.L * (unsigned)G;
         P.sync[3] = sm->epoch + (unsigned)P.L;
         if (P.tp > 1) atomicAdd(P.tp_seq, (unsigned)P.L);
         km_stamp(P, 12);
@@ -876,8 +986,8 @@ static bool km_plan(KmParams &P, int tokens, int H, int I, int grid, int smem_op
     P.p1.rows_total = I; P.p1.up_offset = I;
     const int part_floats = tokens == 1 ? kPartFloats1 : kPartFloats2;
     if (P.p1.TR * 2 * tokens * P.p1.nhw > part_floats) return false;
-    P.R2 = max(1, min(kKmMaxKb, kDefaultStageTarget / (H * 4)));
     P.stage_w_bytes = round_up(2 * P.p1.TR * P.p1.rb, 128);
+    P.R2 = max(1, min(kKmMaxKb, P.stage_w_bytes / (H * 4))); /* k-major rows per stage: about what a gate/up tile takes */
     P.sc_half_bytes = round_up(P.p1.TR * P.p1.G * 2 + 32, 16);
     P.stage_bytes = round_up(max(P.stage_w_bytes + 2 * P.sc_half_bytes, P.R2 * H * 4), 128);
     P.xs_bytes = round_up(tokens * H * 2, 128);
@@ -964,7 +1074,7 @@ int kmajor_ffn_launch(cudaStream_t stream, const void *x, void *act, void *layer
         if (tokens * H > tp->slot_stride) return fail(FFN_ERR_CONFIG, "k-major FFN: %d tokens exceed the exchange buffer", tokens);
     }
     P.norm_eps = eps; P.norm_gemma = gemma;
-    P.trace = nullptr;
+    P.trace = fused_get_trace();
     for (int l0 = 0; l0 < num_layers; l0 += kKmMaxLayers) {
         P.L = min(kKmMaxLayers, num_layers - l0);
         for (int l = 0; l < P.L; ++l) {

@@ -89,6 +89,7 @@ int fused_status_noalloc(unsigned *status_out, bool reset);
 bool fused_noalloc_in_use();
 bool gemv_describe_plan(int tokens, int N, int K, int sm_count, int smem_optin, char *out, size_t out_bytes);
 void fused_set_trace(long long *device_buffer);
+long long *fused_get_trace();
 /* ffn_kmajor.cu: the persistent multi-layer kernel over k-major copies of the down projections
  * (registered per layer with ffn_decode_layer_prepare).  `layers` are `num_layers` consecutive layers
  * of one stack (1 for a single FFN call); with_norm fuses each layer's RMSNorm (post_norm_w) into its

@@ -301,21 +301,20 @@ int ffn_forward_mlp_host(FfnTpComm *comm, void *stream, const void *normed_host,
     if (dims->hidden_size <= 0) return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_host: invalid hidden size");
     const size_t bytes = (size_t)tokens * dims->hidden_size * 2;
     cudaStream_t s = (cudaStream_t)stream;
-    /* Pinned (or registered) host memory is mapped into the device's address space: the kernel reads
-     * its 10 KB of activations and writes its 10 KB of results across PCIe itself, which costs less
-     * than two copy calls.  Pageable memory goes through `staging`. */
+    /* Pinned (or registered) host memory is mapped into the device's address space: the kernel can
+     * write its results across PCIe itself, which costs less than a copy call.  Pageable memory goes
+     * through `staging`. */
     auto mapped = [](const void *p) -> void * {
         cudaPointerAttributes attr;
         if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
         if (attr.type == cudaMemoryTypeUnregistered) return nullptr;
         return attr.devicePointer; /* device and managed memory: the pointer itself */
     };
-    uint16_t *x_dev = (uint16_t *)mapped(normed_host), *y_dev = (uint16_t *)mapped(layer_out_host);
-    const bool stage_in = x_dev == nullptr || ((uintptr_t)x_dev & 15), stage_out = y_dev == nullptr;
-    if (stage_in) {
-        x_dev = (uint16_t *)staging;
-        FFN_CUDA_TRY(cudaMemcpyAsync(x_dev, normed_host, bytes, cudaMemcpyDefault, s), "ffn_forward_mlp_host: input copy");
-    }
+    /* The input is read by every CTA, so it is copied to the device once; the output is written once,
+     * by the CTAs that own its rows, and can go straight to mapped host memory. */
+    uint16_t *x_dev = (uint16_t *)staging, *y_dev = (uint16_t *)mapped(layer_out_host);
+    const bool stage_out = y_dev == nullptr;
+    FFN_CUDA_TRY(cudaMemcpyAsync(x_dev, normed_host, bytes, cudaMemcpyDefault, s), "ffn_forward_mlp_host: input copy");
     if (stage_out) y_dev = (uint16_t *)staging + (size_t)tokens * dims->hidden_size;
     TpComm *c = (TpComm *)comm;
     const int st = (c && c->tp > 1) ? ffn_forward_mlp_tp(comm, stream, x_dev, ws, y_dev, w, tokens, dims, nullptr)
