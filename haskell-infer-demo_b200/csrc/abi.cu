@@ -161,9 +161,15 @@ int ffn_int4_describe_kmajor_plan(int tokens, int hidden, int intermediate, int 
     if (tokens < 1 || hidden <= 0 || intermediate <= 0 || hidden % FFN_INT4_GROUP || intermediate % FFN_INT4_GROUP ||
         sm_count < 1 || smem_optin < 1)
         return fail(FFN_ERR_CONFIG, "ffn_int4_describe_kmajor_plan: invalid shape or device description");
+    if (imma_describe_plan(tokens, hidden, intermediate, sm_count, smem_optin, out, out_bytes)) return FFN_OK;
     if (kmajor_describe_plan(tokens, hidden, intermediate, sm_count, smem_optin, out, out_bytes)) return FFN_OK;
     snprintf(out, out_bytes, "kernel=none (the k-major kernel does not take this shape; the row-major kernels do)");
     return FFN_OK;
+}
+
+int ffn_int4_set_decode_kernel(int which) {
+    if (which != 0 && which != 1) return kmajor_prefer_dp4a(kmajor_prefer_dp4a(0));
+    return kmajor_prefer_dp4a(which);
 }
 
 int ffn_int4_describe_gemm_plan(int m, int n, int k, int sm_count, int smem_optin, char *out, size_t out_bytes) {

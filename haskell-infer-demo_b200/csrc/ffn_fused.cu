@@ -588,7 +588,7 @@ static int launch_fused(DeviceState &d, const FusedParams &P, int grid, size_t s
 int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                      const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual,
                      const FusedNorm *norm) {
-    if (tokens < 1 || tokens > 2) return FFN_NOT_ADMITTED;
+    if (tokens < 1 || tokens > 4) return FFN_NOT_ADMITTED;
     DeviceState *dp = nullptr;
     const int st = device_state(&dp);
     if (st) return st;
@@ -602,6 +602,7 @@ int fused_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *l
                                          with_norm ? norm->eps : 0.0f, with_norm ? norm->gemma : 0, d.sync + 3);
         if (km != FFN_NOT_ADMITTED) return km;
     }
+    if (tokens > 2) return FFN_NOT_ADMITTED; /* the row-major single-launch kernel takes one or two tokens */
     if (((uintptr_t)w->gate_up_i4 & 15) || ((uintptr_t)w->down_i4 & 15) || ((uintptr_t)normed & 15) ||
         ((uintptr_t)act & 15) || ((uintptr_t)w->gate_up_i4_scales & 15) || ((uintptr_t)w->down_i4_scales & 15))
         return FFN_NOT_ADMITTED;

@@ -42,6 +42,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "stream_common.cuh"
+#include "kmajor_common.cuh"
 
 namespace ffn {
 
@@ -123,63 +124,6 @@ __device__ __forceinline__ void km_stamp(const KmParams &P, int slot) {
         P.trace[(size_t)blockIdx.x * 16 + slot] = (long long)t;
     }
 }
-/* first k-block of CTA `cta` (total * ctas < 2^32 is checked on the host) */
-__device__ __forceinline__ int km_begin(int total, int cta, int ctas) {
-    return (int)(((unsigned)total * (unsigned)cta) / (unsigned)ctas);
-}
-
-/* Tag of the words layer number `e` (counted per device since start-up) leaves inside its GPU: never
- * zero (zero marks a word nobody has written), and two consecutive layers never share one, also when
- * the 32-bit count wraps. */
-__device__ __forceinline__ unsigned km_tag(unsigned e) { return e | 0x80000000u; }
-
-/* tagged words inside one GPU: {FP32 value, tag} as one 8-byte relaxed store / load at GPU scope */
-__device__ __forceinline__ unsigned long long km_word(float v, unsigned tag) {
-    return ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
-}
-__device__ __forceinline__ void km_store2(unsigned long long *p, unsigned long long a, unsigned long long b) { /* 16-byte aligned */
-    asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
-}
-__device__ __forceinline__ void km_store1(unsigned long long *p, unsigned long long a) {
-    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
-}
-/* Loads of tagged words come in batches (up to 20 per lane) whose results are all checked afterwards,
- * so they must overlap: plain loads served by the L2 (.cg: no L1 allocation, so a repeated poll reads
- * the L2 again).  Loads qualified .relaxed.gpu measured one L2 round trip EACH, back to back - 6 us for
- * a batch.  A word is only ever accepted on its tag, so a stale answer costs a retry, never an error. */
-__device__ __forceinline__ unsigned long long km_load1(const unsigned long long *p) {
-    unsigned long long w;
-    asm volatile("ld.global.cg.u64 %0, [%1];" : "=l"(w) : "l"(p));
-    return w;
-}
-__device__ __forceinline__ void km_load2(const unsigned long long *p, unsigned long long &a, unsigned long long &b) {
-    asm volatile("ld.global.cg.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p));
-}
-__device__ __forceinline__ unsigned km_load_counter(const unsigned *p) {
-    unsigned v;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void km_arrive_counter(unsigned *p) {
-    asm volatile("red.relaxed.gpu.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
-}
-__device__ __forceinline__ uint2 km_lds8(uint32_t addr) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-    return v;
-}
-
-/* A relaxed counter as a HINT that polling the tagged words is worth starting: waits (bounded) until
- * it has reached `target`.  Correctness never depends on it - the words validate themselves. */
-__device__ __forceinline__ bool km_wait_counter(const unsigned *p, unsigned target, volatile int *abort_flag) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if ((int)(km_load_counter(p) - target) >= 0) return true;
-        if ((i & 63) == 63 && *abort_flag) return false;
-        __nanosleep(40);
-    }
-    return false;
-}
-
 /* The four byte planes of eight block-fixed-point activations X[0..7] (16-bit two's complement in the
  * low halves), laid out for chunk_dot-style dp4a against one widened weight word: he / le pair with
  * the even codes, ho / lo with the odd ones (the layout prepare_chunk builds, stream_common.cuh). */
@@ -703,7 +647,7 @@ __device__ __forceinline__ bool km_consumer_layer(const KmParams &P, KmSmem *sm,
             if (lane == 0) mbar_arrive(&sm->empty[s]);
         }
         /* this CTA's share of every output row, as tagged words */
-        unsigned long long *mine = P.partial + (size_t)blockIdx.x * MT * H;
+        unsigned long long *mine = P.partial + (size_t)blockIdx.x * km_partial_stride(MT, H);
 #pragma unroll
         for (int j = 0; j < kKmMaxPairs; ++j) {
             if (j < npairs && 2 * ti + 2 * kConsumerThreads * j < H) {
@@ -759,13 +703,14 @@ __device__ __forceinline__ bool km_consumer_layer(const KmParams &P, KmSmem *sm,
         unsigned long long w[kKmMaxQ];
         bool in = false;
         uint32_t attempts = 0;
+        if (threadIdx.x == 32 && l == 0 && it0 == 0) km_stamp(P, 15);
         for (uint32_t k = 0; k < kTpPollLimit && !in; ++k) {
             in = true;
             ++attempts;
 #pragma unroll
             for (int i = 0; i < kKmMaxQ; ++i) {
                 w[i] = (unsigned long long)tag << 32; /* value 0.0, tag of this layer */
-                if ((use_mask >> i) & 1u) w[i] = km_load1(P.partial + ((size_t)(s8 + 8 * i) * MT + m) * H + row);
+                if ((use_mask >> i) & 1u) w[i] = km_load1(P.partial + (size_t)(s8 + 8 * i) * km_partial_stride(MT, H) + (size_t)m * H + row);
             }
 #pragma unroll
             for (int i = 0; i < kKmMaxQ; ++i) in = in && (unsigned)(w[i] >> 32) == tag;
@@ -907,12 +852,13 @@ __global__ void km_transpose_scales_kernel(uint16_t *__restrict__ st, const uint
 /* ============================================================================================= */
 /* Host side                                                                                     */
 /* ============================================================================================= */
+constexpr int kKmBufTokens = 4; /* tokens the hand-over buffers are sized for (the tensor-core kernel takes up to four) */
 struct KmDevice {
     bool ready = false;
     int sm_count = 0, smem_optin = 0, cooperative = 0;
     unsigned *sync = nullptr;              /* 4 words */
-    unsigned long long *partial = nullptr; /* [sm_count][2][hidden_cap] */
-    unsigned long long *hx = nullptr;      /* [2][hidden_cap] */
+    unsigned long long *partial = nullptr; /* [sm_count][kKmBufTokens][hidden_cap] */
+    unsigned long long *hx = nullptr;      /* [kKmBufTokens][hidden_cap] */
     int hidden_cap = 0;
     bool attr_set[2][2] = {};
 };
@@ -944,7 +890,7 @@ static int km_device(KmDevice **out, int hidden) {
     if (hidden > d.hidden_cap) { /* first use of a wider model on this device: (re)allocate the hand-over buffers */
         if (d.partial) { FFN_CUDA_TRY(cudaDeviceSynchronize(), "k-major kernel: scratch regrow"); cudaFree(d.partial); cudaFree(d.hx); }
         d.partial = nullptr; d.hx = nullptr; d.hidden_cap = 0;
-        const size_t pw = (size_t)d.sm_count * 2 * hidden, hw = (size_t)2 * hidden;
+        const size_t pw = (size_t)d.sm_count * km_partial_stride(kKmBufTokens, hidden), hw = (size_t)kKmBufTokens * hidden;
         if (cudaMalloc(&d.partial, pw * 8) != cudaSuccess || cudaMalloc(&d.hx, hw * 8) != cudaSuccess) {
             (void)cudaGetLastError();
             if (d.partial) cudaFree(d.partial);
@@ -960,6 +906,26 @@ static int km_device(KmDevice **out, int hidden) {
     return FFN_OK;
 }
 
+int kmajor_device_view(int hidden, int tokens, KmDeviceView *out) {
+    if (tokens > kKmBufTokens) return fail(FFN_ERR_CONFIG, "k-major kernels: at most %d tokens", kKmBufTokens);
+    std::lock_guard<std::mutex> lock(g_km_mutex);
+    KmDevice *d = nullptr;
+    const int st = km_device(&d, hidden);
+    if (st) return st;
+    out->sm_count = d->sm_count; out->smem_optin = d->smem_optin; out->cooperative = d->cooperative;
+    out->sync = d->sync; out->partial = d->partial; out->hx = d->hx;
+    return FFN_OK;
+}
+
+bool kmajor_lookup(const void *down_i4, int hidden, int inter, int dev, const uint32_t **wt, const uint16_t **st) {
+    std::lock_guard<std::mutex> lock(g_km_mutex);
+    const auto it = g_km_layers.find(down_i4);
+    if (it == g_km_layers.end() || it->second.hidden != hidden || it->second.inter != inter || it->second.device != dev) return false;
+    *wt = it->second.wt;
+    *st = it->second.st;
+    return true;
+}
+
 /* Clears the kernel's counters after a launch that gave up (called when the status word is reset). */
 void kmajor_reset_sync() {
     int dev = 0;
@@ -969,8 +935,8 @@ void kmajor_reset_sync() {
     if (!d.ready) return;
     (void)cudaMemset(d.sync, 0, 4 * sizeof(unsigned));
     /* the layer count (the tags' base) starts again at zero, so no word of the interrupted launches may survive */
-    if (d.partial) (void)cudaMemset(d.partial, 0, (size_t)d.sm_count * 2 * d.hidden_cap * 8);
-    if (d.hx) (void)cudaMemset(d.hx, 0, (size_t)2 * d.hidden_cap * 8);
+    if (d.partial) (void)cudaMemset(d.partial, 0, (size_t)d.sm_count * km_partial_stride(kKmBufTokens, d.hidden_cap) * 8);
+    if (d.hx) (void)cudaMemset(d.hx, 0, (size_t)kKmBufTokens * d.hidden_cap * 8);
 }
 
 /* Launch geometry from the shape alone.  Returns false when the kernel does not take it. */
@@ -1033,9 +999,21 @@ static_assert(sizeof(KmParams) <= 4000, "the kernel parameters must fit the 4 KB
 /* `num_layers` layers (1 for a single FFN call) in launches of at most kKmMaxLayers.  Returns
  * FFN_NOT_ADMITTED when a layer has no k-major copy or the shape is outside what the kernel takes;
  * nothing has been launched then. */
+static int g_prefer_dp4a = 0;
+int kmajor_prefer_dp4a(int on) {
+    const int old = g_prefer_dp4a;
+    g_prefer_dp4a = on != 0;
+    return old;
+}
+
 int kmajor_ffn_launch(cudaStream_t stream, const void *x, void *act, void *layer_out, const FfnMlpWeights *layers,
                       int num_layers, int tokens, int H, int I, const FusedTp *tp, void *residual, int with_norm,
                       float eps, int gemma, unsigned *status) {
+    if (!g_prefer_dp4a) { /* the tensor-core consumers first; shapes they do not take fall through to the dp4a kernel */
+        const int st = imma_ffn_launch(stream, x, act, layer_out, layers, num_layers, tokens, H, I, tp, residual, with_norm, eps,
+                                       gemma, status);
+        if (st != FFN_NOT_ADMITTED) return st;
+    }
     if (tokens < 1 || tokens > 2 || num_layers < 1) return FFN_NOT_ADMITTED;
     if (num_layers > 1 && (residual != x || !with_norm)) return FFN_NOT_ADMITTED; /* a stack runs on the residual stream */
     std::lock_guard<std::mutex> lock(g_km_mutex);

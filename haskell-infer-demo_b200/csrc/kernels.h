@@ -98,6 +98,13 @@ int kmajor_ffn_launch(cudaStream_t stream, const void *x, void *act, void *layer
                       int num_layers, int tokens, int H, int I, const FusedTp *tp, void *residual, int with_norm,
                       float eps, int gemma, unsigned *status);
 void kmajor_reset_sync();
+/* ffn_imma.cu: the same contract for 1..4 tokens with the inner products on the INT8 tensor cores.
+ * kmajor_ffn_launch tries it first unless kmajor_prefer_dp4a(1) was called (A/B measurements, tests). */
+int imma_ffn_launch(cudaStream_t stream, const void *x, void *act, void *layer_out, const FfnMlpWeights *layers,
+                    int num_layers, int tokens, int H, int I, const FusedTp *tp, void *residual, int with_norm,
+                    float eps, int gemma, unsigned *status);
+bool imma_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin, char *out, size_t out_bytes);
+int kmajor_prefer_dp4a(int on); /* returns the previous setting */
 bool kmajor_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin, char *out, size_t out_bytes);
 /* ffn_mma.cu: the tensor-core path for 3..64 tokens (two launches: gate/up + SiLU*up, down + reduce). */
 int mma_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,

@@ -370,7 +370,7 @@ int ffn_decode_stack(FfnTpComm *comm, void *stream, void *h, void *ws, void *lay
     const int H = dims->hidden_size, I = dims->intermediate_size;
     if (H <= 0 || I <= 0 || H % FFN_INT4_GROUP || I % FFN_INT4_GROUP)
         return fail(FFN_ERR_CONFIG, "ffn_decode_stack: hidden=%d / intermediate=%d are not whole numbers of %d-wide groups", H, I, FFN_INT4_GROUP);
-    if (tokens <= 2 && num_layers > 0) {
+    if (tokens <= 4 && num_layers > 0) {
         /* every layer prepared with ffn_decode_layer_prepare: the whole stack in one persistent launch per 64 layers */
         bool whole = dims->rms_eps > 0.0f;
         for (int l = 0; l < num_layers && whole; ++l)

@@ -245,6 +245,13 @@ int ffn_decode_layer_is_prepared(const FfnMlpWeights *w); /* 1 or 0 */
 int ffn_int4_describe_kmajor_plan(int tokens, int hidden, int intermediate, int sm_count, int smem_optin, char *out,
                                   size_t out_bytes);
 
+/* Which of the two kernels over k-major copies serves 1-2 token calls: 0 (default) the one whose inner
+ * products run on the INT8 tensor cores (mma.sync m16n8k32, activations as two signed byte planes of
+ * 15-bit block fixed point), falling back to 1, the dp4a kernel (16-bit block fixed point), for shapes
+ * it does not take; 1 forces the dp4a kernel.  Both are CUDA paths held to the same bars; the switch
+ * exists for A/B measurement and for the tests.  Returns the previous setting. */
+int ffn_int4_set_decode_kernel(int which);
+
 /* The fused FFN (as ffn_forward_mlp_prepared, 1 or 2 tokens) for callers that cannot allocate
  * device memory: a host that handed all of the GPU's memory to its own arena at start-up, so a
  * cudaMalloc from inside a library would fail, or a decode loop that cannot take the device-wide

@@ -79,7 +79,8 @@ def _cached_layer(hidden, inter, row):
 
 
 @pytest.mark.parametrize("hidden,inter", [(1024, 3072), (5120, 17408)])
-@pytest.mark.parametrize("tokens,kmajor", [(1, False), (2, False), (8, False), (16, False), (1, True), (2, True)])
+@pytest.mark.parametrize("tokens,kmajor", [(1, False), (2, False), (8, False), (16, False), (1, True), (2, True), (4, True),
+                                           (1, "dp4a"), (2, "dp4a")])
 def test_ffn_second_projection_is_exact_on_a_one_hot_act(cuda, hidden, inter, tokens, kmajor):
     """The whole FFN call (single-launch kernel for 1-2 tokens - row-major, or over the k-major copy of
     the down projection - and the tensor-core pair for 8 and 16) on a
@@ -91,10 +92,14 @@ def test_ffn_second_projection_is_exact_on_a_one_hot_act(cuda, hidden, inter, to
     layer, deq_down = _cached_layer(hidden, inter, live[0])
     rng = np.random.default_rng(tokens)
     x = o.bf16_round(rng.standard_normal((tokens, hidden), dtype=np.float32))
-    mlp = upload_layer(layer, cuda, prepare=kmajor)
+    mlp = upload_layer(layer, cuda, prepare=bool(kmajor))
     ws = mlp.workspace(tokens)
-    y = mlp.forward_mlp_prepared(dev_bf16(x, cuda), ws=ws)
-    L.device_status()
+    old = L.load().ffn_int4_set_decode_kernel(1 if kmajor == "dp4a" else 0)
+    try:
+        y = mlp.forward_mlp_prepared(dev_bf16(x, cuda), ws=ws)
+        L.device_status()
+    finally:
+        L.load().ffn_int4_set_decode_kernel(old)
     act_dev = host_f32(ws[tokens * (hidden + 2 * inter):tokens * (hidden + 3 * inter)].view(tokens, inter))
     _, _, act_cpu = o.ffn(layer, x, intermediates=True)
     off = act_dev.copy()
@@ -107,15 +112,16 @@ def test_ffn_second_projection_is_exact_on_a_one_hot_act(cuda, hidden, inter, to
     assert same.all(), f"H={hidden} I={inter} M={tokens}: {np.count_nonzero(~same)} outputs differ"
 
 
-@pytest.mark.parametrize("tokens,kmajor", [(1, False), (2, False), (8, False), (1, True), (2, True)])
+@pytest.mark.parametrize("tokens,kmajor", [(1, False), (2, False), (8, False), (1, True), (2, True), (3, True), (1, "dp4a"), (2, "dp4a")])
 def test_ffn_first_projection_is_exact_on_a_one_hot_input(cuda, tokens, kmajor):
     """One-hot x: gate and up are single products, so act may differ from the CPU chain only through
     __expf (at most one BF16 ulp, and on few elements)."""
     hidden, inter = 1024, 3072
     _, layers = o.draw_config(hidden, inter, 17, tokens=tokens)
     layer = layers[0]
-    mlp = upload_layer(layer, cuda, prepare=kmajor)
+    mlp = upload_layer(layer, cuda, prepare=bool(kmajor))
     ws = mlp.workspace(tokens)
+    L.load().ffn_int4_set_decode_kernel(1 if kmajor == "dp4a" else 0)
     for step in range(8):
         x = np.zeros((tokens, hidden), np.float32)
         for m in range(tokens):
@@ -127,6 +133,7 @@ def test_ffn_first_projection_is_exact_on_a_one_hot_input(cuda, tokens, kmajor):
         ulp = np.maximum(np.abs(act_cpu), 2.0 ** -100) * 2.0 ** -7
         assert np.all(np.abs(act_dev - act_cpu) <= ulp)
         assert np.count_nonzero(act_dev != act_cpu) <= act_cpu.size // 50
+    L.load().ffn_int4_set_decode_kernel(0)
 
 
 @pytest.mark.parametrize("tokens", [1, 2, 8])

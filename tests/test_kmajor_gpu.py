@@ -22,6 +22,15 @@ SHAPES = [(1024, 3072, 0), (2560, 9728, 1), (5120, 17408, 2),
           (2560, 4864, 8), (6528, 1024, 9)]   # the widest hidden size the kernel takes
 
 
+@pytest.fixture(params=[0, 1], ids=["tensor-core", "dp4a"], autouse=True)
+def decode_kernel(request):
+    """Every test of this file runs twice: with the tensor-core (INT8 MMA) consumers, which is the
+    default, and with the dp4a kernel forced (ffn_int4_set_decode_kernel)."""
+    old = L.load().ffn_int4_set_decode_kernel(request.param)
+    yield request.param
+    L.load().ffn_int4_set_decode_kernel(old)
+
+
 @pytest.fixture(scope="module")
 def drawn():
     cache = {}
@@ -36,15 +45,17 @@ def drawn():
     return get
 
 
-@pytest.mark.parametrize("tokens", [1, 2])
+@pytest.mark.parametrize("tokens", [1, 2, 3, 4])
 @pytest.mark.parametrize("hidden,inter,seed", SHAPES)
-def test_kmajor_ffn_matches_oracle(cuda, drawn, hidden, inter, seed, tokens):
+def test_kmajor_ffn_matches_oracle(cuda, drawn, decode_kernel, hidden, inter, seed, tokens):
+    if tokens > 2 and decode_kernel == 1:
+        pytest.skip("the dp4a kernel takes one or two tokens")
     x, layer, want = drawn(hidden, inter, seed, tokens)
     mlp = upload_layer(layer, cuda, prepare=True)
     assert L.load().ffn_decode_layer_is_prepared(ctypes.byref(mlp.weights)) == 1
     plan = ctypes.create_string_buffer(1024)
     L.check(L.load().ffn_int4_describe_kmajor_plan(tokens, hidden, inter, 148, 232448, plan, 1024))
-    assert b"kernel=kmajor" in plan.value, plan.value
+    assert b"kernel=imma" in plan.value or b"kernel=kmajor" in plan.value, plan.value
     xd = dev_bf16(x, cuda)
     ws = mlp.workspace(tokens)
     got_t = mlp.forward_mlp_prepared(xd, ws=ws)
@@ -83,8 +94,10 @@ def test_kernels_alternate_on_one_device(cuda, drawn):
         assert_ffn_close(got, want, f"H={h} I={i} M={tokens} prepared={prep} in a mixed sequence")
 
 
-@pytest.mark.parametrize("tokens,nlayers", [(1, 12), (2, 7)])
-def test_kmajor_stack_one_launch(cuda, tokens, nlayers):
+@pytest.mark.parametrize("tokens,nlayers", [(1, 12), (2, 7), (4, 5)])
+def test_kmajor_stack_one_launch(cuda, decode_kernel, tokens, nlayers):
+    if tokens > 2 and decode_kernel == 1:
+        pytest.skip("the dp4a kernel takes one or two tokens")
     """The stack in ONE persistent launch: teacher-forced per layer at the FFN bars, free-running
     within the oracle-vs-oracle spread, equal bit for bit to the same layers launched one by one, and
     to itself when run again."""
