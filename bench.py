@@ -216,6 +216,8 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     L.load()
+    if args.no_overlap:
+        L.load().ffn_int4_set_launch_overlap(0)
     tp, m, h, i = world, args.tokens, HIDDEN, INTER
     per_rank_bytes = algorithmic_bytes(h, i, tp)
     stack = args.layers > 0
@@ -230,7 +232,7 @@ def run_ours(args):
         copies = max(2, int(2.2 * L2_BYTES / per_rank_bytes) + 1)
         layers = [synth.stack_layer_torch(2, c, h, i, tp, rank, dev, with_norm=False) for c in range(copies)]
         x = synth.stack_input_torch(2, m, h, dev)
-    if not args.row_major:  # k-major copies of the down projections: the decode kernel without the phase barrier
+    if args.kmajor:  # k-major copies of the down projections: the decode kernel without the phase barrier
         for lay in layers:
             lay.prepare()
     use_nccl = world > 1 and args.exchange == "nccl"
@@ -352,7 +354,7 @@ def run_ours(args):
     parity = None
     if not args.no_parity:
         parity = parity_stack(dev, layers, comm, tp, h, i, m, x) if stack else \
-            parity_single_layer(dev, comm, tp, rank, h, i, m, use_nccl, not args.row_major)
+            parity_single_layer(dev, comm, tp, rank, h, i, m, use_nccl, args.kmajor)
         if world > 1 and parity.get("ok") is not None:
             flag = torch.tensor([1 if parity["ok"] else 0], device=dev)
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
@@ -370,9 +372,10 @@ def run_ours(args):
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
         gbs = nl * per_rank_bytes / us_step / 1e3
-        per_layer = 1 if m <= 2 else (4 if stack else 3)
+        kmajor = m <= 2 and args.kmajor   # layers with k-major copies: the persistent decode kernel
+        per_layer = 1 if (m <= 2 or kmajor) else (4 if stack else 3)
         launches = nl * per_layer
-        if stack and m <= 2 and not args.row_major:
+        if stack and kmajor:
             launches = -(-nl // 64)          # the whole stack in one persistent launch per 64 layers
         line = {
             "metric": METRIC, "value": round(us_step, 3), "unit": "us/step", "n_gpus": world,
@@ -386,7 +389,8 @@ def run_ours(args):
                                     f"H={h} I={i} M={m} TP={tp} (BASELINE configs[4])"),
                        "l2": (f"rotating {copies} different layers per rank ({copies * per_rank_bytes / 1e6:.0f} MB > 2x L2)" if not stack else
                               f"{copies} layers = {copies * per_rank_bytes / 1e6:.0f} MB per rank, each read once per step"),
-                       "timing": f"{args.steps} steps in one CUDA graph, median of {reps} replays, max over ranks"},
+                       "timing": f"{args.steps} steps in one CUDA graph, median of {reps} replays, max over ranks",
+                       "launch_overlap": not args.no_overlap},
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
                          "frac": round(gbs / peak, 4), "peak_source": peak_kind, "traffic": captured_traffic(tp, m, args.layers),
                          "algorithmic_bytes_per_launch": per_rank_bytes * nl / launches, "launches_per_step": launches},
@@ -394,8 +398,8 @@ def run_ours(args):
                     "d2h_bytes_per_step": m * h * 2,
                     "through": "ffn_forward_mlp_host" if not (stack or use_nccl) else "copy, call, copy, synchronise issued by the caller"},
             "gpu_launches": args.steps * launches,
-            "kernel": ("k-major decode kernel (persistent, no phase barrier)" if (m <= 2 and not args.row_major) else
-                       "row-major single-launch kernel" if m <= 2 else "tensor-core pair (mma.sync)"),
+            "kernel": ("persistent decode kernel over k-major down projections (dp4a)" if kmajor else
+                       "row-major single-launch kernel (dp4a)" if m <= 2 else "batched pair (mma.sync bf16)"),
             "exchange": ("none (one GPU)" if world == 1 else "in-kernel tagged-word exchange over NVLink peer memory"
                          if not use_nccl else "comparison variant: NCCL all-reduce of the BF16 output after the kernel"),
             "parity": parity,
@@ -544,9 +548,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle comparison of the timed workload")
-    ap.add_argument("--row-major", action="store_true",
-                    help="do not register k-major copies of the down projections: one or two tokens then run the row-major "
-                         "single-launch kernel (one launch per layer)")
+    ap.add_argument("--kmajor", action="store_true",
+                    help="comparison variant: register k-major copies of the down projections, so that one or two tokens "
+                         "run the persistent decode kernel (a whole stack in one launch) instead of the row-major "
+                         "single-launch kernel, which measured faster and is the default")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="comparison variant: launch without the programmatic-dependent-launch attribute")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1 only. fused: the cross-rank sum inside the FFN kernel (the product). nccl: comparison "
                          "variant - the same kernel per rank without an exchange, then an NCCL all-reduce of the BF16 "

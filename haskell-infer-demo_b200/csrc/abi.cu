@@ -168,8 +168,21 @@ int ffn_int4_describe_kmajor_plan(int tokens, int hidden, int intermediate, int 
 }
 
 int ffn_int4_set_decode_kernel(int which) {
-    if (which != 0 && which != 1) return kmajor_prefer_dp4a(kmajor_prefer_dp4a(0));
+    if (which != 0 && which != 1) { /* a query: leaves the setting as it is */
+        const int current = kmajor_prefer_dp4a(1);
+        kmajor_prefer_dp4a(current);
+        return current;
+    }
     return kmajor_prefer_dp4a(which);
+}
+
+int ffn_int4_set_launch_overlap(int on) {
+    if (on != 0 && on != 1) {
+        const int current = fused_set_launch_overlap(1);
+        fused_set_launch_overlap(current);
+        return current;
+    }
+    return fused_set_launch_overlap(on);
 }
 
 int ffn_int4_describe_gemm_plan(int m, int n, int k, int sm_count, int smem_optin, char *out, size_t out_bytes) {

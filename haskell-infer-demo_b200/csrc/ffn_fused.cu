@@ -70,6 +70,8 @@ struct FusedParams {
     float norm_eps;
     int norm_gemma;
     long long *trace;     /* optional [kTraceWords] clock64 stamps of CTA 0 (NULL = off) */
+    int early_weights;    /* 1: the first fill of every stage is issued before the wait on the previous launch of
+                             the stream (set by the host together with the dependent-launch attribute) */
     int gemv;             /* 1: single-matrix mode - only phase 2 runs, its activation is the caller's input
                              (no grid barrier, nothing handed over between phases) */
 #ifdef FFN_INT4_TUNING
@@ -345,6 +347,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ns = P.nstages;
 
+    if (threadIdx.x == 0) griddep_launch(); /* the next launch may take this CTA's SM the moment it is free */
     if (warp == 0) {
         if (lane == 0) stamp(P, 0);
         if (lane < ns) { mbar_init(&sm->full[lane], 1); mbar_init(&sm->empty[lane], kConsumerWarps); }
@@ -363,13 +366,49 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
     if (warp == 0) {
         /* ---------------- producer ---------------- */
         if (lane == 0) {
+            const int total = nt1 + nt2;
+            int t = 0;
+            auto issue_tile = [&](int t) {
+                const int s = t % ns;
+                uint8_t *dst = ring + (size_t)s * P.stage_bytes;
+                if (FFN_DEBUG_BIT(P, 2)) { mbar_arrive(&sm->full[s]); return; }
+                if (t < nt1) {
+                    const int r0 = b1 + t * P.p1.TR, rows = min(P.p1.TR, e1 - r0);
+                    const uint32_t bytes = (uint32_t)rows * P.p1.rb;
+                    /* scale runs widened to 16-byte boundaries (the array's end is one: row counts
+                     * are multiples of 8, so N*G*2 is a multiple of 16) */
+                    const size_t g0 = (size_t)r0 * P.p1.G * 2, g1 = (size_t)(r0 + P.p1.up_offset) * P.p1.G * 2;
+                    const size_t len = (size_t)rows * P.p1.G * 2;
+                    const size_t a0 = g0 & ~(size_t)15, a1 = g1 & ~(size_t)15;
+                    const uint32_t n0 = (uint32_t)(((g0 + len + 15) & ~(size_t)15) - a0);
+                    const uint32_t n1 = (uint32_t)(((g1 + len + 15) & ~(size_t)15) - a1);
+                    mbar_expect_tx(&sm->full[s], 2 * bytes + n0 + n1);
+                    bulk_g2s(dst, P.p1.w + (size_t)r0 * P.p1.rb, bytes, &sm->full[s]);
+                    bulk_g2s(dst + bytes, P.p1.w + (size_t)(r0 + P.p1.up_offset) * P.p1.rb, bytes, &sm->full[s]);
+                    bulk_g2s(dst + P.stage_w_bytes, (const uint8_t *)P.p1.s + a0, n0, &sm->full[s]);
+                    bulk_g2s(dst + P.stage_w_bytes + P.sc_half_bytes, (const uint8_t *)P.p1.s + a1, n1, &sm->full[s]);
+                } else {
+                    const int r0 = b2 + (t - nt1) * P.p2.TR, rows = min(P.p2.TR, e2 - r0);
+                    const uint32_t bytes = (uint32_t)rows * P.p2.rb;
+                    const size_t g0 = (size_t)r0 * P.p2.G * 2, len = (size_t)rows * P.p2.G * 2;
+                    const size_t a0 = g0 & ~(size_t)15;
+                    const uint32_t n0 = (uint32_t)(((g0 + len + 15) & ~(size_t)15) - a0);
+                    mbar_expect_tx(&sm->full[s], bytes + n0);
+                    bulk_g2s(dst, P.p2.w + (size_t)r0 * P.p2.rb, bytes, &sm->full[s]);
+                    bulk_g2s(dst + P.stage_w_bytes, (const uint8_t *)P.p2.s + a0, n0, &sm->full[s]);
+                }
+            };
+            /* The weights never change, so the first fill of every stage need not wait for the launch
+             * before this one in the stream: with programmatic dependent launch this CTA starts as soon
+             * as its SM is free, and these copies are in flight while the previous grid drains. */
+            if (P.early_weights)
+                for (; t < min(ns, total); ++t) issue_tile(t);
+            griddep_wait();
             /* grid barrier: every CTA adds one to a monotonic counter; the launch's target is the
              * count the previous launch left behind plus this grid's size (stable during the launch,
              * so replaying a captured graph or changing the grid size needs no host bookkeeping) */
             const unsigned bar_target = P.sync[1] + gridDim.x;
             stamp(P, 1);
-            const int total = nt1 + nt2;
-            int t = 0;
             bool act_issued = false, failed = false;
             /* Phase 2's activation vector is fetched once the grid barrier has opened (every CTA has
              * stored its rows of act). */
@@ -399,33 +438,7 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
                     failed = true;
                     break;
                 }
-                uint8_t *dst = ring + (size_t)s * P.stage_bytes;
-                if (FFN_DEBUG_BIT(P, 2)) { mbar_arrive(&sm->full[s]); continue; }
-                if (t < nt1) {
-                    const int r0 = b1 + t * P.p1.TR, rows = min(P.p1.TR, e1 - r0);
-                    const uint32_t bytes = (uint32_t)rows * P.p1.rb;
-                    /* scale runs widened to 16-byte boundaries (the array's end is one: row counts
-                     * are multiples of 8, so N*G*2 is a multiple of 16) */
-                    const size_t g0 = (size_t)r0 * P.p1.G * 2, g1 = (size_t)(r0 + P.p1.up_offset) * P.p1.G * 2;
-                    const size_t len = (size_t)rows * P.p1.G * 2;
-                    const size_t a0 = g0 & ~(size_t)15, a1 = g1 & ~(size_t)15;
-                    const uint32_t n0 = (uint32_t)(((g0 + len + 15) & ~(size_t)15) - a0);
-                    const uint32_t n1 = (uint32_t)(((g1 + len + 15) & ~(size_t)15) - a1);
-                    mbar_expect_tx(&sm->full[s], 2 * bytes + n0 + n1);
-                    bulk_g2s(dst, P.p1.w + (size_t)r0 * P.p1.rb, bytes, &sm->full[s]);
-                    bulk_g2s(dst + bytes, P.p1.w + (size_t)(r0 + P.p1.up_offset) * P.p1.rb, bytes, &sm->full[s]);
-                    bulk_g2s(dst + P.stage_w_bytes, (const uint8_t *)P.p1.s + a0, n0, &sm->full[s]);
-                    bulk_g2s(dst + P.stage_w_bytes + P.sc_half_bytes, (const uint8_t *)P.p1.s + a1, n1, &sm->full[s]);
-                } else {
-                    const int r0 = b2 + (t - nt1) * P.p2.TR, rows = min(P.p2.TR, e2 - r0);
-                    const uint32_t bytes = (uint32_t)rows * P.p2.rb;
-                    const size_t g0 = (size_t)r0 * P.p2.G * 2, len = (size_t)rows * P.p2.G * 2;
-                    const size_t a0 = g0 & ~(size_t)15;
-                    const uint32_t n0 = (uint32_t)(((g0 + len + 15) & ~(size_t)15) - a0);
-                    mbar_expect_tx(&sm->full[s], bytes + n0);
-                    bulk_g2s(dst, P.p2.w + (size_t)r0 * P.p2.rb, bytes, &sm->full[s]);
-                    bulk_g2s(dst + P.stage_w_bytes, (const uint8_t *)P.p2.s + a0, n0, &sm->full[s]);
-                }
+                issue_tile(t);
             }
             if (!act_issued && !failed && !P.gemv) fetch_act();
             /* Never leave with a copy of ours still in flight: wait (bounded) for the most recent
@@ -443,10 +456,12 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
         }
     } else if (warp <= kConsumerWarps) {
         /* ---------------- consumers ---------------- */
+        griddep_wait(); /* the input may be the previous kernel's output */
         if (!P.gemv) consume_phase<CIT1, MT, true>(P, P.p1, sm, xs, ring, 0);
         if (!sm->abort_flag) consume_phase<CIT2, MT, false>(P, P.p2, sm, xs, ring, nt1);
     } else {
         /* ---------------- epilogue ---------------- */
+        griddep_wait(); /* act, out, the residual and the exchange slots may still be in use by the previous launch */
         /* read before this CTA arrives at the grid barrier: nobody can have advanced it yet */
         const unsigned seq = P.tp > 1 ? ld_acquire_gpu(P.tp_seq) : 0u;
         bool ok = true;
@@ -470,19 +485,8 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
                 for (int i = lane; i < (e2 - b2) * MT; i += 32) {
                     const int row = b2 + i / MT, m = i % MT;
                     float a = 0.0f;
-                    bool all_in = true;
-                    for (int r = 0; r < P.tp && all_in; ++r) {
-                        const unsigned long long *p = mine + (size_t)r * P.slot_stride + (size_t)m * P.H + row;
-                        float v = 0.0f;
-                        bool in = tp_load_tagged(p, tp_tag(seq), &v);
-                        for (uint32_t k = 0; !in && k < kTpPollLimit; ++k) {
-                            if ((k & 1023u) == 1023u && sm->abort_flag) break; /* another lane already gave up */
-                            __nanosleep(20);
-                            in = tp_load_tagged(p, tp_tag(seq), &v);
-                        }
-                        all_in = in;
-                        a += v;
-                    }
+                    const bool all_in = tp_wait_sum(mine + (size_t)m * P.H + row, (size_t)P.slot_stride, P.tp, tp_tag(seq),
+                                                    &sm->abort_flag, 20, &a);
                     if (!all_in) { give_up(sm, P.sync, ST_PEER_DATA); break; }
                     const float y = round_bf16(a);
                     P.out[(size_t)m * P.H + row] = f32_to_bf16_bits(y);
@@ -514,6 +518,7 @@ struct DeviceState {
     int cooperative = 0;
     unsigned *sync = nullptr; /* 4 words: count, generation, sequence, status */
     bool attr_set[2][2][2] = {};
+    int overlap_ok = 0; /* dependent launch next to a cooperative one: 0 not tried yet, 1 taken, -1 refused */
 };
 static DeviceState g_dev[64];
 static long long *g_trace = nullptr; /* debugging aid: device buffer for CTA 0's clock stamps */
@@ -521,6 +526,12 @@ static long long *g_trace = nullptr; /* debugging aid: device buffer for CTA 0's
 void fused_set_trace(long long *device_buffer) { g_trace = device_buffer; }
 long long *fused_get_trace() { return g_trace; }
 static std::mutex g_dev_mutex;
+static int g_launch_overlap = 1;
+int fused_set_launch_overlap(int on) {
+    const int old = g_launch_overlap;
+    g_launch_overlap = on != 0;
+    return old;
+}
 
 static int device_state(DeviceState **out) {
     int dev = 0;
@@ -569,7 +580,7 @@ static bool plan_fused(FusedParams &P, int tokens, int H, int I, int smem_optin,
 }
 
 template <int C1, int C2, int MT>
-static int launch_fused(DeviceState &d, const FusedParams &P, int grid, size_t smem, cudaStream_t stream) {
+static int launch_fused(DeviceState &d, const FusedParams &P_in, int grid, size_t smem, cudaStream_t stream) {
     {
         std::lock_guard<std::mutex> lock(g_dev_mutex);
         bool &set = d.attr_set[C1 - 1][C2 - 1][MT - 1];
@@ -578,6 +589,45 @@ static int launch_fused(DeviceState &d, const FusedParams &P, int grid, size_t s
                                               d.smem_optin), "fused FFN: shared-memory opt-in");
             set = true;
         }
+    }
+    FusedParams P = P_in;
+    /* Programmatic dependent launch: consecutive launches in one stream overlap this launch's start
+     * (CTA scheduling, barrier set-up, the first weight copies) with the tail of the one before.
+     * Whether the driver takes the attribute next to a cooperative launch is found out once per
+     * device, outside stream capture; until then, and wherever it is refused, the launch is the
+     * plain cooperative one. */
+    int overlap = 0;
+    if (g_launch_overlap && !P.gemv) {
+        if (d.overlap_ok == 1) {
+            overlap = 1;
+        } else if (d.overlap_ok == 0) {
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) overlap = 2; /* probe */
+        }
+    }
+    if (overlap) {
+        P.early_weights = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attrs[2];
+        attrs[0].id = cudaLaunchAttributeCooperative;
+        attrs[0].val.cooperative = 1;
+        attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attrs;
+        cfg.numAttrs = 2;
+        const cudaError_t err = cudaLaunchKernelEx(&cfg, ffn_fused_kernel<C1, C2, MT>, P);
+        if (err == cudaSuccess) {
+            if (overlap == 2) d.overlap_ok = 1;
+            return FFN_OK;
+        }
+        if (overlap == 1) return fail(FFN_ERR_CUDA, "fused FFN launch: %s", cudaGetErrorString(err));
+        (void)cudaGetLastError(); /* the probe was refused: remember, and launch the plain way */
+        d.overlap_ok = -1;
+        P.early_weights = 0;
     }
     void *args[] = {(void *)&P};
     FFN_CUDA_TRY(cudaLaunchCooperativeKernel((const void *)ffn_fused_kernel<C1, C2, MT>, dim3(grid), dim3(kThreads),

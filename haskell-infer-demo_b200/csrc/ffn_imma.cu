@@ -184,6 +184,10 @@ __device__ __forceinline__ int im_build_chunks(int kb0, int kb1, int *ckb, int *
  * copy (the rows are skewed by 16 bytes in shared memory), then the two runs of their scales.
  * Phase-2 tile (slab, chunk): the chunk's k-major rows, restricted to the slab's output columns. */
 __device__ __forceinline__ void im_producer(const ImParams &P, ImSmem *sm, uint8_t *ring, int kb0, int kb1) {
+    /* The whole warp: lane 0 waits for the stage and posts the byte count, then every lane issues one
+     * of the tile's copies (a single thread issuing eighteen 2.5 KB copies per tile cannot keep up with
+     * the HBM stream). */
+    const int lane = threadIdx.x & 31;
     const int ns = P.nstages;
     const int nt1 = kb1 - kb0;
     int ckb[kImMaxChunks], cn[kImMaxChunks], cseg[kImMaxChunks], nseg = 0;
@@ -196,41 +200,44 @@ __device__ __forceinline__ void im_producer(const ImParams &P, ImSmem *sm, uint8
         const ImLayer &LY = P.layers[l];
         for (int lt = 0; lt < nt1 + nt2; ++lt, ++t) {
             const int s = t % ns;
-            if (t >= ns && !mbar_wait<100>(&sm->empty[s], (uint32_t)(t / ns - 1) & 1u, &sm->abort_flag)) {
-                im_give_up(sm, P.status, ST_PRODUCER_EMPTY);
+            bool ok = true;
+            if (lane == 0 && t >= ns) ok = mbar_wait<100>(&sm->empty[s], (uint32_t)(t / ns - 1) & 1u, &sm->abort_flag);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+                if (lane == 0) im_give_up(sm, P.status, ST_PRODUCER_EMPTY);
                 failed = true;
                 break;
             }
             uint8_t *dst = ring + (size_t)s * P.stage_bytes;
             if (lt < nt1) {
-                const int r0 = (kb0 + lt) * 8; /* first pair of the tile */
-                const size_t g0 = (size_t)r0 * Gs * 2, g1 = (size_t)(r0 + P.I) * Gs * 2, len = (size_t)8 * Gs * 2;
-                const size_t a0 = g0 & ~(size_t)15, a1 = g1 & ~(size_t)15;
-                const uint32_t n0 = (uint32_t)(((g0 + len + 15) & ~(size_t)15) - a0);
-                const uint32_t n1 = (uint32_t)(((g1 + len + 15) & ~(size_t)15) - a1);
-                mbar_expect_tx(&sm->full[s], 16u * (uint32_t)P.rb1 + n0 + n1);
-#pragma unroll 1
-                for (int r = 0; r < 8; ++r) {
-                    bulk_g2s(dst + (size_t)r * P.rs1, LY.gu_w + (size_t)(r0 + r) * P.rb1, (uint32_t)P.rb1, &sm->full[s]);
-                    bulk_g2s(dst + (size_t)(8 + r) * P.rs1, LY.gu_w + (size_t)(P.I + r0 + r) * P.rb1, (uint32_t)P.rb1, &sm->full[s]);
-                }
-                bulk_g2s(dst + P.sc_off, (const uint8_t *)LY.gu_s + a0, n0, &sm->full[s]);
-                bulk_g2s(dst + P.sc_off + P.sc_half_bytes, (const uint8_t *)LY.gu_s + a1, n1, &sm->full[s]);
+                const int r0 = (kb0 + lt) * 8; /* first pair of the tile; 8 * Gs * 2 bytes of scales per run, 16-byte aligned */
+                const uint32_t nsc = (uint32_t)(8 * Gs * 2);
+                if (lane == 0) mbar_expect_tx(&sm->full[s], 16u * (uint32_t)P.rb1 + 2u * nsc);
+                __syncwarp();
+                if (lane < 8)
+                    bulk_g2s(dst + (size_t)lane * P.rs1, LY.gu_w + (size_t)(r0 + lane) * P.rb1, (uint32_t)P.rb1, &sm->full[s]);
+                else if (lane < 16)
+                    bulk_g2s(dst + (size_t)lane * P.rs1, LY.gu_w + (size_t)(P.I + r0 + lane - 8) * P.rb1, (uint32_t)P.rb1, &sm->full[s]);
+                else if (lane == 16)
+                    bulk_g2s(dst + P.sc_off, (const uint8_t *)LY.gu_s + (size_t)r0 * Gs * 2, nsc, &sm->full[s]);
+                else if (lane == 17)
+                    bulk_g2s(dst + P.sc_off + P.sc_half_bytes, (const uint8_t *)LY.gu_s + (size_t)(r0 + P.I) * Gs * 2, nsc, &sm->full[s]);
             } else {
                 const int tt = lt - nt1, sl = tt / nch, ch = tt % nch;
                 const int c0 = sl * P.slab, cols = min(P.slab, P.H - c0);
-                mbar_expect_tx(&sm->full[s], (uint32_t)cn[ch] * (uint32_t)cols * 4u);
-#pragma unroll 1
-                for (int r = 0; r < cn[ch]; ++r)
-                    bulk_g2s(dst + (size_t)r * P.rs2, LY.wt + (size_t)(ckb[ch] + r) * P.H + c0, (uint32_t)cols * 4u, &sm->full[s]);
+                if (lane == 0) mbar_expect_tx(&sm->full[s], (uint32_t)cn[ch] * (uint32_t)cols * 4u);
+                __syncwarp();
+                if (lane < cn[ch])
+                    bulk_g2s(dst + (size_t)lane * P.rs2, LY.wt + (size_t)(ckb[ch] + lane) * P.H + c0, (uint32_t)cols * 4u, &sm->full[s]);
             }
         }
     }
-    for (int u = max(0, t - ns); u < t; ++u) { /* never leave with a copy of ours still in flight */
-        bool done = false;
-        for (uint32_t i = 0; i < kSpinLimit && !done; ++i) done = mbar_try_wait(&sm->full[u % ns], (uint32_t)(u / ns) & 1u);
-        if (!done) atomicCAS(P.status, 0u, (unsigned)ST_DRAIN | ((unsigned)blockIdx.x << 8));
-    }
+    if (lane == 0)
+        for (int u = max(0, t - ns); u < t; ++u) { /* never leave with a copy of ours still in flight */
+            bool done = false;
+            for (uint32_t i = 0; i < kSpinLimit && !done; ++i) done = mbar_try_wait(&sm->full[u % ns], (uint32_t)(u / ns) & 1u);
+            if (!done) atomicCAS(P.status, 0u, (unsigned)ST_DRAIN | ((unsigned)blockIdx.x << 8));
+        }
 }
 
 /* ---- consumers: the layer's input ------------------------------------------------------------------ */
@@ -812,10 +819,8 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_imma_kernel(const __grid_cons
     const int nt1 = kb1 - kb0;
 
     if (warp == 0) {
-        if (lane == 0) {
-            im_stamp(P, 1);
-            im_producer(P, sm, ring, kb0, kb1);
-        }
+        if (lane == 0) im_stamp(P, 1);
+        im_producer(P, sm, ring, kb0, kb1);
     } else if (warp <= kConsumerWarps) {
         /* phase-2 tiles per layer: chunks x slabs (the chunk count follows from the K range alone) */
         int ckb[kImMaxChunks], cn[kImMaxChunks], cseg[kImMaxChunks], nseg = 0;

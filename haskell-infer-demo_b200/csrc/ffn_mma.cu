@@ -302,18 +302,7 @@ __global__ void __launch_bounds__(kMmaThreads) down_mma_kernel(const MmaParams P
             const int r = i % kMmaRows, m = i / kMmaRows;
             const size_t o = (size_t)m * P.N + row0 + r;
             float y = 0.0f;
-            bool all_in = true;
-            for (int q = 0; q < P.tp && all_in; ++q) {
-                const unsigned long long *p = mine + (size_t)q * P.slot_stride + o;
-                float v = 0.0f;
-                bool in = tp_load_tagged(p, tp_tag(seq), &v);
-                for (uint32_t k = 0; !in && k < kTpPollLimit; ++k) {
-                    __nanosleep(40);
-                    in = tp_load_tagged(p, tp_tag(seq), &v);
-                }
-                all_in = in;
-                y += v;
-            }
+            const bool all_in = tp_wait_sum(mine + o, (size_t)P.slot_stride, P.tp, tp_tag(seq), nullptr, 40, &y);
             if (!all_in) { atomicCAS(P.status, 0u, 6u | ((unsigned)blockIdx.x << 8)); break; } /* 6 = peer data */
             const float v = round_bf16(y);
             P.out[o] = f32_to_bf16_bits(v);

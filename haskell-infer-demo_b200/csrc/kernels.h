@@ -52,9 +52,13 @@ constexpr uint32_t kTpPollLimit = 1u << 20; /* polls of one tagged word before a
  * written since the buffer was cleared), also when the 32-bit call counter wraps. */
 __host__ __device__ __forceinline__ unsigned tp_tag(unsigned seq) { return seq % 0xFFFFFFFFu + 1u; }
 
+/* A plain 8-byte store (one transaction, posted over NVLink): a store qualified .relaxed.sys is
+ * completed before the thread's next strong access issues - measured as one full round trip per
+ * store inside a GPU - which would put a link round trip in front of every following store and of
+ * the first poll.  The receiver accepts a word on its tag only, so nothing else has to be ordered. */
 __device__ __forceinline__ void tp_store_tagged(unsigned long long *p, float v, unsigned tag) {
     const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
-    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+    asm volatile("st.global.cg.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 /* true when the word carries `tag`; *v is its value then */
 __device__ __forceinline__ bool tp_load_tagged(const unsigned long long *p, unsigned tag, float *v) {
@@ -62,6 +66,36 @@ __device__ __forceinline__ bool tp_load_tagged(const unsigned long long *p, unsi
     asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
     *v = __uint_as_float((unsigned)w);
     return (unsigned)(w >> 32) == tag;
+}
+
+/* Waits (bounded) until the `tp` words first[r * stride] all carry `tag`, then returns their values added
+ * in rank order.  All loads of a round are issued before any tag is looked at, so they overlap (plain
+ * loads served by the L2, where writes arriving over NVLink land; a load qualified .relaxed.sys is
+ * completed before the next one issues, which made eight ranks cost eight round trips). */
+__device__ __forceinline__ bool tp_wait_sum(const unsigned long long *first, size_t stride, int tp, unsigned tag,
+                                            const volatile int *abort_flag, uint32_t sleep_ns, float *sum) {
+    unsigned long long w[kTpMaxRanks];
+    bool in = false;
+    for (uint32_t k = 0; k < kTpPollLimit && !in; ++k) {
+        in = true;
+#pragma unroll
+        for (int r = 0; r < kTpMaxRanks; ++r) {
+            w[r] = (unsigned long long)tag << 32;
+            if (r < tp) asm volatile("ld.global.cg.u64 %0, [%1];" : "=l"(w[r]) : "l"(first + (size_t)r * stride));
+        }
+#pragma unroll
+        for (int r = 0; r < kTpMaxRanks; ++r) in = in && (unsigned)(w[r] >> 32) == tag;
+        if (!in) {
+            if ((k & 1023u) == 1023u && abort_flag && *abort_flag) break;
+            __nanosleep(sleep_ns);
+        }
+    }
+    float a = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kTpMaxRanks; ++r)
+        if (r < tp) a += __uint_as_float((unsigned)w[r]);
+    *sum = a;
+    return in;
 }
 
 /* Tensor-parallel exchange tables (device arrays of per-rank pointers, set up once at load). */
@@ -98,8 +132,10 @@ int kmajor_ffn_launch(cudaStream_t stream, const void *x, void *act, void *layer
                       int num_layers, int tokens, int H, int I, const FusedTp *tp, void *residual, int with_norm,
                       float eps, int gemma, unsigned *status);
 void kmajor_reset_sync();
+int fused_set_launch_overlap(int on); /* ffn_fused.cu: programmatic dependent launch on or off; returns the previous setting */
 /* ffn_imma.cu: the same contract for 1..4 tokens with the inner products on the INT8 tensor cores.
- * kmajor_ffn_launch tries it first unless kmajor_prefer_dp4a(1) was called (A/B measurements, tests). */
+ * kmajor_ffn_launch tries it first only after kmajor_prefer_dp4a(0) (A/B measurements, tests): it measured
+ * slower than the dp4a kernel, which is the default. */
 int imma_ffn_launch(cudaStream_t stream, const void *x, void *act, void *layer_out, const FfnMlpWeights *layers,
                     int num_layers, int tokens, int H, int I, const FusedTp *tp, void *residual, int with_norm,
                     float eps, int gemma, unsigned *status);

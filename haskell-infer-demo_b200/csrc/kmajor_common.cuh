@@ -25,15 +25,18 @@ __host__ __device__ __forceinline__ size_t km_partial_stride(int tokens, int hid
  * the 32-bit count wraps. */
 __device__ __forceinline__ unsigned km_tag(unsigned e) { return e | 0x80000000u; }
 
-/* tagged words inside one GPU: {FP32 value, tag} as one 8-byte relaxed store / load at GPU scope */
+/* tagged words inside one GPU: {FP32 value, tag} as one 8-byte store / load */
 __device__ __forceinline__ unsigned long long km_word(float v, unsigned tag) {
     return ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
 }
+/* Plain stores that go to the L2 (.cg): stores qualified .relaxed.gpu measured a full L2 round trip
+ * each, one after the other (40 stores = 12 us); the readers accept a word on its tag only, so no
+ * ordering between the stores is needed. */
 __device__ __forceinline__ void km_store2(unsigned long long *p, unsigned long long a, unsigned long long b) { /* 16-byte aligned */
-    asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+    asm volatile("st.global.cg.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
 }
 __device__ __forceinline__ void km_store1(unsigned long long *p, unsigned long long a) {
-    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
+    asm volatile("st.global.cg.u64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
 }
 /* Loads of tagged words come in batches (up to 20 per lane) whose results are all checked afterwards,
  * so they must overlap: plain loads served by the L2 (.cg: no L1 allocation, so a repeated poll reads

@@ -245,12 +245,26 @@ int ffn_decode_layer_is_prepared(const FfnMlpWeights *w); /* 1 or 0 */
 int ffn_int4_describe_kmajor_plan(int tokens, int hidden, int intermediate, int sm_count, int smem_optin, char *out,
                                   size_t out_bytes);
 
-/* Which of the two kernels over k-major copies serves 1-2 token calls: 0 (default) the one whose inner
- * products run on the INT8 tensor cores (mma.sync m16n8k32, activations as two signed byte planes of
- * 15-bit block fixed point), falling back to 1, the dp4a kernel (16-bit block fixed point), for shapes
- * it does not take; 1 forces the dp4a kernel.  Both are CUDA paths held to the same bars; the switch
- * exists for A/B measurement and for the tests.  Returns the previous setting. */
+/* Which of the two kernels over k-major copies serves calls on prepared layers: 1 (default) the dp4a
+ * kernel (16-bit block fixed point per 32 values, 1-2 tokens); 0 the variant whose inner products run
+ * on the INT8 tensor cores (mma.sync m16n8k32, activations as two signed byte planes of 15-bit block
+ * fixed point per 128 values, 1-4 tokens), falling back to the dp4a kernel for shapes it does not take.
+ * The tensor-core variant measured slower on B200 (legacy mma.sync integer rate) and its coarser fixed
+ * point leaves rare elements two BF16 steps from the reference's value over a 64-layer stack, so it is
+ * opt-in and kept for A/B measurement.  Returns the previous setting. */
 int ffn_int4_set_decode_kernel(int which);
+
+/* Overlap of consecutive FFN launches in one stream (default 1, on).  The fused FFN kernel is launched
+ * with the programmatic-dependent-launch attribute: the next launch's CTAs are scheduled onto SMs as
+ * this launch's CTAs leave them, set up their barriers and start the first copies of the weight stream,
+ * and only then wait for this launch to complete before they touch the input, the workspace, the
+ * output or the exchange slots.  The weight copies issued before that wait read the INT4 operands and
+ * their scales, which therefore must not be written by the kernel that directly precedes the call in
+ * the stream (the reference loads them once at start-up: csrc/safetensors_loader.cu); every other
+ * operand may be.  0 turns the attribute off (plain cooperative launches, as CUDA orders them); any
+ * other value queries.  Returns the previous setting.  The reference has no counterpart: its launches
+ * are ordered by the stream alone (csrc/kernels/layers.cu:164, forward_mlp_prepared). */
+int ffn_int4_set_launch_overlap(int on);
 
 /* The fused FFN (as ffn_forward_mlp_prepared, 1 or 2 tokens) for callers that cannot allocate
  * device memory: a host that handed all of the GPU's memory to its own arena at start-up, so a

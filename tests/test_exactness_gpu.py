@@ -121,7 +121,7 @@ def test_ffn_first_projection_is_exact_on_a_one_hot_input(cuda, tokens, kmajor):
     layer = layers[0]
     mlp = upload_layer(layer, cuda, prepare=bool(kmajor))
     ws = mlp.workspace(tokens)
-    L.load().ffn_int4_set_decode_kernel(1 if kmajor == "dp4a" else 0)
+    old = L.load().ffn_int4_set_decode_kernel(1 if kmajor == "dp4a" else 0)
     for step in range(8):
         x = np.zeros((tokens, hidden), np.float32)
         for m in range(tokens):
@@ -133,7 +133,7 @@ def test_ffn_first_projection_is_exact_on_a_one_hot_input(cuda, tokens, kmajor):
         ulp = np.maximum(np.abs(act_cpu), 2.0 ** -100) * 2.0 ** -7
         assert np.all(np.abs(act_dev - act_cpu) <= ulp)
         assert np.count_nonzero(act_dev != act_cpu) <= act_cpu.size // 50
-    L.load().ffn_int4_set_decode_kernel(0)
+    L.load().ffn_int4_set_decode_kernel(old)
 
 
 @pytest.mark.parametrize("tokens", [1, 2, 8])

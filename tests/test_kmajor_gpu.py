@@ -24,8 +24,8 @@ SHAPES = [(1024, 3072, 0), (2560, 9728, 1), (5120, 17408, 2),
 
 @pytest.fixture(params=[0, 1], ids=["tensor-core", "dp4a"], autouse=True)
 def decode_kernel(request):
-    """Every test of this file runs twice: with the tensor-core (INT8 MMA) consumers, which is the
-    default, and with the dp4a kernel forced (ffn_int4_set_decode_kernel)."""
+    """Every test of this file runs twice: with the dp4a kernel, which is the default for prepared
+    layers, and with the opt-in tensor-core (INT8 MMA) consumers (ffn_int4_set_decode_kernel)."""
     old = L.load().ffn_int4_set_decode_kernel(request.param)
     yield request.param
     L.load().ffn_int4_set_decode_kernel(old)
@@ -55,7 +55,8 @@ def test_kmajor_ffn_matches_oracle(cuda, drawn, decode_kernel, hidden, inter, se
     assert L.load().ffn_decode_layer_is_prepared(ctypes.byref(mlp.weights)) == 1
     plan = ctypes.create_string_buffer(1024)
     L.check(L.load().ffn_int4_describe_kmajor_plan(tokens, hidden, inter, 148, 232448, plan, 1024))
-    assert b"kernel=imma" in plan.value or b"kernel=kmajor" in plan.value, plan.value
+    if tokens <= 2:      # (three and four tokens fall back to the batched pair where the tensor-core kernel has no room)
+        assert b"kernel=imma" in plan.value or b"kernel=kmajor" in plan.value, plan.value
     xd = dev_bf16(x, cuda)
     ws = mlp.workspace(tokens)
     got_t = mlp.forward_mlp_prepared(xd, ws=ws)
