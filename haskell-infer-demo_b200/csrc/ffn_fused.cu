@@ -613,10 +613,10 @@ static int launch_fused(DeviceState &d, const FusedParams &P_in, int grid, size_
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
         cudaLaunchAttribute attrs[2];
-        attrs[0].id = cudaLaunchAttributeCooperative;
-        attrs[0].val.cooperative = 1;
-        attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attrs[1].val.programmaticStreamSerializationAllowed = 1;
+        attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[0].val.programmaticStreamSerializationAllowed = 1;
+        attrs[1].id = cudaLaunchAttributeCooperative;
+        attrs[1].val.cooperative = 1;
         cfg.attrs = attrs;
         cfg.numAttrs = 2;
         const cudaError_t err = cudaLaunchKernelEx(&cfg, ffn_fused_kernel<C1, C2, MT>, P);
