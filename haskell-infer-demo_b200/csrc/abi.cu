@@ -61,7 +61,7 @@ static int mlp_common(cudaStream_t stream, const void *normed, void *ws, void *l
         bool taken = true;
         for (int m0 = 0; m0 < tokens && taken; m0 += 64) {
             const int m = tokens - m0 < 64 ? tokens - m0 : 64;
-            st = mma_ffn_launch(stream, (const uint16_t *)normed + (size_t)m0 * H, act + (size_t)m0 * I,
+            st = batched_ffn_launch(stream, (const uint16_t *)normed + (size_t)m0 * H, act + (size_t)m0 * I,
                                 (uint16_t *)layer_out + (size_t)m0 * H, w, m, H, I, nullptr, nullptr, status);
             if (st == FFN_NOT_ADMITTED) { taken = false; break; }
             if (st) return st;
@@ -143,7 +143,8 @@ int ffn_int4_describe_plan(int tokens, int hidden, int intermediate, int sm_coun
         sm_count < 1 || smem_optin < 1)
         return fail(FFN_ERR_CONFIG, "ffn_int4_describe_plan: invalid shape or device description");
     if (tokens <= 2 && fused_describe_plan(tokens, hidden, intermediate, sm_count, smem_optin, out, out_bytes)) return FFN_OK;
-    if (mma_describe_plan(tokens < 64 ? tokens : 64, hidden, intermediate, sm_count, smem_optin, out, out_bytes)) {
+    if (tc_describe_plan(tokens < 64 ? tokens : 64, hidden, intermediate, sm_count, smem_optin, out, out_bytes) ||
+        mma_describe_plan(tokens < 64 ? tokens : 64, hidden, intermediate, sm_count, smem_optin, out, out_bytes)) {
         if (tokens > 64) { /* longer batches go through the pair in blocks of 64 tokens */
             const size_t used = strlen(out);
             snprintf(out + used, out_bytes - used, " passes=%d", (tokens + 63) / 64);
@@ -174,6 +175,15 @@ int ffn_int4_set_decode_kernel(int which) {
         return current;
     }
     return kmajor_prefer_dp4a(which);
+}
+
+int ffn_int4_set_batched_kernel(int which) {
+    if (which != 0 && which != 1) { /* a query */
+        const int enabled = tc_set_enabled(1);
+        tc_set_enabled(enabled);
+        return enabled ? 0 : 1;
+    }
+    return tc_set_enabled(which == 0) ? 0 : 1;
 }
 
 int ffn_int4_set_launch_overlap(int on) {
@@ -211,7 +221,11 @@ static int report_status(unsigned st, int *where, int *cta) {
                                       "consumer waiting for a partial slot", "epilogue waiting for partials",
                                       "grid barrier", "a peer rank's partial sums", "draining copies",
                                       "consumer waiting for the activation vector", "waiting for the other CTAs' partial sums",
-                                      "waiting for the residual stream of the next layer", "waiting for this CTA's own activations"};
+                                      "waiting for the residual stream of the next layer", "waiting for this CTA's own activations",
+                                      "", "", "", "", "", "", "", "",
+                                      "tcgen05 producer waiting for a free stage", "tcgen05 kernel waiting for a stage's copies",
+                                      "conversion warps waiting for a free operand buffer", "MMA thread waiting for a converted operand",
+                                      "MMA thread waiting for a free accumulator", "epilogue waiting for an accumulator"};
         const unsigned w = st & 0xFF;
         return fail(FFN_ERR_CUDA, "a bounded device-side wait ran out (%s, CTA %u); the kernel returned early and "
                     "its output is invalid", w < sizeof(names) / sizeof(names[0]) ? names[w] : "unknown", st >> 8);

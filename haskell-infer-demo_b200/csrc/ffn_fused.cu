@@ -857,6 +857,7 @@ int fused_status(unsigned *status_out, bool reset) {
     if (reset && words[3] != 0) {
         FFN_CUDA_TRY(cudaMemset(dp->sync, 0, sizeof(words)), "reset synchronisation words");
         kmajor_reset_sync();
+        tc_reset_sync();
     }
     return FFN_OK;
 }

@@ -257,7 +257,7 @@ int ffn_forward_mlp_tp(FfnTpComm *comm, void *stream, const void *normed, void *
     if (st == FFN_NOT_ADMITTED && tokens <= 64) {
         unsigned *status = nullptr;
         if ((st = fused_status_word(&status))) return st;
-        st = mma_ffn_launch((cudaStream_t)stream, normed, act, layer_out, w, tokens, H, I, &t, residual, status);
+        st = batched_ffn_launch((cudaStream_t)stream, normed, act, layer_out, w, tokens, H, I, &t, residual, status);
     }
     if (st == FFN_NOT_ADMITTED)
         return fail(FFN_ERR_CONFIG, "ffn_forward_mlp_tp: the fused kernel does not take this shape (tokens=%d H=%d I=%d)", tokens, H, I);
@@ -351,7 +351,7 @@ static int decode_layer(TpComm *c, cudaStream_t stream, void *h, void *ws, void 
     if (st) return st;
     unsigned *status = nullptr;
     if ((st = fused_status_word(&status))) return st;
-    st = mma_ffn_launch(stream, normed, act, layer_out, w, tokens, H, I, tp, h, status);
+    st = batched_ffn_launch(stream, normed, act, layer_out, w, tokens, H, I, tp, h, status);
     if (st == FFN_NOT_ADMITTED) return fail(FFN_ERR_CONFIG, "ffn_decode_layer: no kernel takes tokens=%d H=%d I=%d", tokens, H, I);
     return st;
 }

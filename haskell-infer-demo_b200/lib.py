@@ -50,6 +50,7 @@ def _declare(lib):
         "ffn_int4_set_fused": [ci],
         "ffn_int4_set_decode_kernel": [ci],
         "ffn_int4_set_launch_overlap": [ci],
+        "ffn_int4_set_batched_kernel": [ci],
         "ffn_gemm_int4_bf16": [vp, vp, vp, vp, ci, ci, ci, ci, vp],
         "ffn_silu_mul_packed": [vp, vp, ci, ci, vp],
         "ffn_gemma_rms_norm": [vp, vp, vp, ci, ci, cf, vp],

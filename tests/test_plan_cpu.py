@@ -29,7 +29,7 @@ def test_fused_plan_respects_the_kernel_limits(hidden, inter, tp, tokens):
         pytest.skip("the split is not a whole number of groups; the loader refuses it")
     p = plan(tokens, hidden, local)
     if p["kernel"] != "fused":
-        assert p["kernel"] in ("mma_pair", "generic")       # a shape the single-launch kernel does not take
+        assert p["kernel"] in ("tcgen05_pair", "mma_pair", "generic")       # a shape the single-launch kernel does not take
         return
     assert p["grid"] == SMS and p["threads"] == 608
     assert p["smem"] <= SMEM and p["stages"] >= 2
@@ -65,6 +65,22 @@ def test_batched_plan(tokens, hidden, inter, tp):
     slots = SMS * p["ctas_per_sm"]
     eff = lambda u: u / (-(-u // slots) * slots)
     assert eff(p["down_ctas"]) >= eff(hidden // 128) - 1e-9
+    # the opt-in tcgen05 pair: admitted while four operand buffers fit next to two packed stages
+    old = L.load().ffn_int4_set_batched_kernel(0)
+    try:
+        p = plan(tokens, hidden, local)
+    finally:
+        L.load().ffn_int4_set_batched_kernel(old)
+    if tokens > 48:
+        assert p["kernel"] == "mma_pair"
+        return
+    assert p["kernel"] == "tcgen05_pair"
+    assert p["token_columns"] >= tokens and p["token_columns"] % 16 == 0 and p["token_columns"] <= 64
+    assert p["smem"] <= SMEM and p["stages"] >= 2 and p["threads"] == 544 and p["operand_buffers"] == 4
+    assert p["accumulator_buffers"] * p["token_columns"] <= p["tmem_columns"] <= 512
+    assert p["gate_up_units"] * 64 == local and p["gate_up_ctas"] == min(p["gate_up_units"], SMS)
+    assert p["down_units"] == (hidden // 128) * p["down_k_splits"] <= SMS
+    assert 1 <= p["down_k_splits"] <= 8 and p["down_k_splits"] * 2 <= max(local // 128, 2)
 
 
 def test_long_batches_run_in_blocks_of_64_and_small_devices_fall_back():
