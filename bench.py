@@ -218,6 +218,8 @@ def run_ours(args):
     L.load()
     if args.no_overlap:
         L.load().ffn_int4_set_launch_overlap(0)
+    if args.batched_kernel:
+        L.load().ffn_int4_set_batched_kernel({"tcgen05": 0, "mma.sync": 1}[args.batched_kernel])
     tp, m, h, i = world, args.tokens, HIDDEN, INTER
     per_rank_bytes = algorithmic_bytes(h, i, tp)
     stack = args.layers > 0
@@ -399,7 +401,10 @@ def run_ours(args):
                     "through": "ffn_forward_mlp_host" if not (stack or use_nccl) else "copy, call, copy, synchronise issued by the caller"},
             "gpu_launches": args.steps * launches,
             "kernel": ("persistent decode kernel over k-major down projections (dp4a)" if kmajor else
-                       "row-major single-launch kernel (dp4a)" if m <= 2 else "batched pair (mma.sync bf16)"),
+                       "row-major single-launch kernel (dp4a)" if m <= 2 else
+                       "batched pair (tcgen05, accumulators and converted operand in tensor memory)"
+                       if L.load().ffn_int4_set_batched_kernel(-1) == 0 or (L.load().ffn_int4_set_batched_kernel(-1) == 2 and m > 32)
+                       else "batched pair (mma.sync bf16)"),
             "exchange": ("none (one GPU)" if world == 1 else "in-kernel tagged-word exchange over NVLink peer memory"
                          if not use_nccl else "comparison variant: NCCL all-reduce of the BF16 output after the kernel"),
             "parity": parity,
@@ -552,6 +557,8 @@ def main():
                     help="comparison variant: register k-major copies of the down projections, so that one or two tokens "
                          "run the persistent decode kernel (a whole stack in one launch) instead of the row-major "
                          "single-launch kernel, which measured faster and is the default")
+    ap.add_argument("--batched-kernel", default="", choices=["", "tcgen05", "mma.sync"],
+                    help="3..64 tokens: which pair of kernels runs (default: the library's own choice)")
     ap.add_argument("--no-overlap", action="store_true",
                     help="comparison variant: launch without the programmatic-dependent-launch attribute")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],

@@ -178,12 +178,12 @@ int ffn_int4_set_decode_kernel(int which) {
 }
 
 int ffn_int4_set_batched_kernel(int which) {
-    if (which != 0 && which != 1) { /* a query */
-        const int enabled = tc_set_enabled(1);
-        tc_set_enabled(enabled);
-        return enabled ? 0 : 1;
+    if (which < 0 || which > 2) { /* a query */
+        const int mode = tc_set_mode(2);
+        tc_set_mode(mode);
+        return mode;
     }
-    return tc_set_enabled(which == 0) ? 0 : 1;
+    return tc_set_mode(which);
 }
 
 int ffn_int4_set_launch_overlap(int on) {

@@ -15,15 +15,20 @@
  *   warps 0-3   epilogue: tcgen05.ld of a finished group (warp w reads lanes 32w..32w+31: thread =
  *               weight row), scale, accumulate; at the end of a unit SiLU(gate)*up or the split-K
  *               hand-over and the output / cross-rank exchange.
- *   warp 4      producer: per stage two tiled TMA loads (cp.async.bulk.tensor.2d, 64 rows x 128 bytes of
+ *   warp 4      producer (one thread): per stage two tiled TMA loads (cp.async.bulk.tensor.2d, 64 rows x 128 bytes of
  *               packed codes each, 128-byte swizzle so the conversion warps read without bank conflicts)
  *               and one bulk copy of the stage's slice of the activations, completion on mbarriers.
- *   warp 5      allocates tensor memory; one thread issues the MMAs (8 per group, K = 16 each) and
- *               commits them to the mbarriers that free the operands and publish the accumulator.
- *   warps 6-13  conversion: INT4 codes of the stage -> BF16 in the MMA's shared-memory operand layout
- *               (K-major, 128-byte swizzle), a ring of two to four buffers of one group each.
- * Four accumulator buffers of N columns rotate between the MMA thread and the epilogue, so the MMAs
- * of group g+1 run while group g is read out.
+ *   warps 5-12  conversion: INT4 codes of the stage -> exact BF16 codes, written from registers straight
+ *               into tensor memory (tcgen05.st), where the MMA reads its A operand: no shared-memory
+ *               copy of the 4x larger BF16 tile, so shared memory is all ring.  Two teams of four
+ *               warps work on two groups at a time.
+ *   warps 13-16 one thread each issues the MMAs (8 per group, K = 16, A from tensor memory, B = the
+ *               stage's activation slice in shared memory) of every fourth group and commits them to
+ *               the mbarriers that publish the accumulator and free the operands; warp 13 also
+ *               allocates and frees tensor memory.
+ * Tensor memory (512 columns): four accumulators of N FP32 columns and four operand buffers of 64
+ * columns; group g uses accumulator, operand buffer and barriers g mod 4, so the MMAs of the next
+ * groups run while group g is read out and group g+4 is converted.
  *
  * Activations are read in "tile order": K in blocks of 64 values; within a block token n owns a
  * 128-byte row at (n/8)*1024 + (n%8)*128 whose 16-byte piece c (8 values of K) sits at piece c ^ (n%8),
@@ -55,12 +60,12 @@ constexpr int kTcRows = 128;                  /* weight rows per unit = the MMA'
 constexpr int kTcGroupsPerStage = 2;
 constexpr int kTcGroupBytes = FFN_INT4_GROUP / 2;                       /* 64 packed bytes per row and group */
 constexpr int kTcRowPitch = kTcGroupsPerStage * kTcGroupBytes;          /* 128: one row of a stage = the TMA box's inner extent = the 128-byte swizzle span */
-constexpr int kTcMaxStages = 3;               /* ring of packed stages: 2 or 3, whatever shared memory leaves room for */
-constexpr int kTcMaxABufs = 4;                /* converted operand buffers: 2 to 4 */
-constexpr int kTcKBlockBytes = kTcRows * 128;                           /* 16384: 128 rows x 64 values of K in BF16, one swizzled K block */
-constexpr int kTcABytes = 2 * kTcKBlockBytes;                           /* 32768: one group (128 values of K) of 128 rows */
+constexpr int kTcMaxStages = 8;               /* ring of packed stages: as many as shared memory holds, at most 8 */
+constexpr int kTcABufs = 4;                   /* converted operand buffers in tensor memory, one per MMA-issuing thread */
 constexpr int kTcAccBufs = 4;
-constexpr int kTcTmemCols = 256;              /* 4 buffers of up to 64 FP32 columns */
+constexpr int kTcACols = FFN_INT4_GROUP / 2;  /* 64 columns of tensor memory hold one group of a row in BF16 (two values per column) */
+constexpr int kTcAFirstCol = 256;             /* columns 0..255: 4 accumulators of up to 64 FP32 columns; 256..511: 4 operand buffers */
+constexpr int kTcTmemCols = 512;
 constexpr int kTcEpiWarps = 4, kTcConvWarps = 8, kTcMmaWarps = 4;
 constexpr int kTcConvTeams = 2;               /* conversion teams of 4 warps: team t converts the groups with index = t mod 2 */
 constexpr int kTcTeamWarps = kTcConvWarps / kTcConvTeams;
@@ -68,15 +73,17 @@ constexpr int kTcProducerWarp = kTcEpiWarps, kTcFirstConvWarp = kTcEpiWarps + 1,
 constexpr int kTcThreads = (kTcFirstMmaWarp + kTcMmaWarps) * 32;        /* 544 */
 constexpr int kTcMaxSplits = 8;
 constexpr int kTcHeader = 5120;               /* barriers, flags, the 64 x 17 exchange buffer of the pairs epilogue */
+constexpr int kTcScaleGroups = 64;            /* groups of scales the epilogue keeps in shared memory at a time: [64][128 rows] bf16 */
+constexpr int kTcScaleBytes = kTcScaleGroups * kTcRows * 2;
 constexpr int kTcBoxRows = 64;                /* rows per TMA box: the gate half and the up half of a unit are separate row ranges */
 
 /* where a bounded wait gave up (status word, low byte), continuing the decode kernels' numbering */
 enum { ST_TC_STAGE_EMPTY = 20, ST_TC_STAGE_FULL = 21, ST_TC_A_EMPTY = 22, ST_TC_A_READY = 23, ST_TC_D_EMPTY = 24, ST_TC_D_FULL = 25 };
-static_assert(kTcMaxABufs <= kTcAccBufs, "a group's `done` barrier must outlive the reuse of its operand buffer");
+static_assert(kTcABufs == kTcAccBufs, "group g uses operand buffer, accumulator and `done` barrier g mod 4");
 
 struct TcSmem {
     uint64_t full[kTcMaxStages], empty[kTcMaxStages];
-    uint64_t a_ready[kTcMaxABufs];          /* a converted operand buffer is complete (one arrival per warp of the team) */
+    uint64_t a_ready[kTcABufs];             /* a converted operand buffer is complete (one arrival per warp of the team) */
     uint64_t done[kTcAccBufs];              /* the MMAs of a group have completed: its accumulator can be read, its operand buffer reused */
     uint64_t d_empty[kTcAccBufs];           /* the epilogue has read the accumulator out */
     uint32_t tmem_base;
@@ -95,7 +102,7 @@ struct TcParams {
     int N, K;                 /* pairs launch: gate/up pairs of this rank; down launch: output rows.  K: columns */
     int up_offset;            /* pairs launch: row of up row 0 */
     int units, splits;        /* units of 128 rows (x K splits for the down launch) */
-    int stages, abufs;        /* depth of the packed ring and of the converted-operand ring */
+    int stages;               /* depth of the packed ring */
     uint16_t *act;            /* pairs: bf16 [M][N] natural order */
     uint8_t *act_t;           /* pairs: the same in tile order (input of the down launch) */
     uint16_t *out;            /* down: bf16 [M][N] */
@@ -131,11 +138,19 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-/* D[tmem] (+)= A[smem] * B[smem]: M = 128, N and the operand types from the instruction descriptor, K = 16 */
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+/* D[tmem] (+)= A[tmem] * B[smem]: M = 128 (lane = row), N and the operand types from the instruction
+ * descriptor, K = 16; one column of A = two consecutive values of K in BF16 */
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+/* 16 consecutive columns of this thread's lane */
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+                   "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 /* 16 consecutive FP32 columns of this thread's lane */
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&d)[16]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -149,10 +164,6 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, i
                  ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); } /* the four epilogue warps */
 
 /* Shared-memory operand descriptor: K-major, 128-byte swizzle.  A row of the operand is 128 bytes (64
@@ -182,6 +193,15 @@ __device__ __forceinline__ uint32_t tc_codes(uint32_t w_shifted) {
 __device__ __forceinline__ int tc_permute8(int e) { return ((e & 3) << 1) | (e >> 2); }
 /* byte offset of token n's 16-byte piece c inside one K block of the activations' tile order */
 __host__ __device__ __forceinline__ int tc_tile_offset(int n, int c) { return (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) << 4); }
+
+/* Bounded wait of a whole warp: one lane polls, the result reaches the others through a shuffle (which
+ * also orders their later accesses after the poll).  Thirty-two lanes polling the same barrier word
+ * only multiply the shared-memory traffic that every other warp's loads and arrivals queue behind. */
+__device__ __forceinline__ bool tc_warp_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int lane) {
+    int ok = 1;
+    if (lane == 0) ok = mbar_wait<32>(bar, parity, abort_flag) ? 1 : 0;
+    return __shfl_sync(~0u, ok, 0) != 0;
+}
 
 struct TcUnit {
     int row_a, row_b;   /* weight rows of lanes 0-63 and 64-127 */
@@ -244,16 +264,16 @@ template <int NT, bool PAIRS>
 __global__ void __launch_bounds__(kTcThreads, 1) ffn_tc_kernel(const __grid_constant__ TcParams P) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     TcSmem *sm = (TcSmem *)smem_raw;
-    uint8_t *abuf = smem_raw + kTcHeader;
-    uint8_t *ring = abuf + (size_t)P.abufs * kTcABytes;
-    const uint32_t nstages = (uint32_t)P.stages, nabufs = (uint32_t)P.abufs;
+    uint16_t *sc_t = (uint16_t *)(smem_raw + kTcHeader); /* the epilogue's scales: [group][row] */
+    uint8_t *ring = smem_raw + kTcHeader + kTcScaleBytes;
+    const uint32_t nstages = (uint32_t)P.stages;
     constexpr int NPAD = NT * 16;
     constexpr int kStageBytes = kTcRows * kTcRowPitch + kTcGroupsPerStage * NPAD * 256;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (warp == kTcProducerWarp && lane == 0) {
-        for (int i = 0; i < kTcMaxStages; ++i) { mbar_init(&sm->full[i], 1); mbar_init(&sm->empty[i], kTcConvWarps + kTcGroupsPerStage); }
-        for (int i = 0; i < kTcMaxABufs; ++i) mbar_init(&sm->a_ready[i], kTcTeamWarps);
+        for (int i = 0; i < kTcMaxStages; ++i) { mbar_init(&sm->full[i], 1); mbar_init(&sm->empty[i], kTcTeamWarps + kTcGroupsPerStage); }
+        for (int i = 0; i < kTcABufs; ++i) mbar_init(&sm->a_ready[i], kTcTeamWarps);
         for (int i = 0; i < kTcAccBufs; ++i) { mbar_init(&sm->done[i], 1); mbar_init(&sm->d_empty[i], kTcEpiWarps); }
         sm->abort_flag = 0;
         sm->last_arrival = 0;
@@ -306,57 +326,68 @@ __global__ void __launch_bounds__(kTcThreads, 1) ffn_tc_kernel(const __grid_cons
         __syncwarp();
     } else if (warp >= kTcFirstConvWarp && warp < kTcFirstMmaWarp) {
         /* ---------------- conversion: INT4 -> BF16 operand tiles ---------------- */
-        /* Two teams of four warps; team t converts the groups whose running index is t mod 2, so two
-         * groups are in conversion at a time.  A thread owns one weight row of its team's group. */
+        /* Two teams of four warps; team t converts the stages whose running index is t mod 2 (both groups
+         * of the stage, so the barrier traffic is paid once per stage), and the two teams work on two
+         * stages at a time.  A thread owns one weight row = one lane of tensor memory; a warp reaches
+         * the 32 lanes of quadrant (warp index mod 4), and the four warps of a team cover the four
+         * quadrants.  The converted row (64 columns = 128 BF16 codes per group) goes straight from
+         * registers to tensor memory, where the MMA reads its A operand. */
         const int cw = warp - kTcFirstConvWarp;
         const uint32_t team = (uint32_t)(cw / kTcTeamWarps);
-        const int row = (cw % kTcTeamWarps) * 32 + lane;
-        const uint32_t a_off = (uint32_t)(row * 128); /* (row >> 3) * 1024 + (row & 7) * 128 */
-        uint32_t it = 0, gi = 0;
+        const int row = (warp & 3) * 32 + lane;
+        const uint32_t a_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)kTcAFirstCol;
+        const bool stamps = lane == 0 && (cw % kTcTeamWarps) == 0;
+        uint32_t it = 0, gi = 0, slot = 0, round = 0; /* slot = it mod stages, round = it div stages */
         bool ok = true;
         for (int u = blockIdx.x; u < P.units && ok; u += gridDim.x) {
             const TcUnit t = tc_unit<PAIRS>(P, u);
-            for (int g = t.g0; g < t.g1 && ok; g += kTcGroupsPerStage, ++it) {
+            for (int g = t.g0; g < t.g1 && ok; g += kTcGroupsPerStage) {
                 const int ng = min(kTcGroupsPerStage, t.g1 - g);
-                const uint32_t slot = it % nstages;
-                if (!mbar_wait<32>(&sm->full[slot], (it / nstages) & 1u, &sm->abort_flag)) {
-                    tc_give_up(sm, P.status, ST_TC_STAGE_FULL);
-                    ok = false;
-                    break;
-                }
-                /* 128-byte swizzle: 16-byte piece c of row r sits at piece c ^ (r & 7) of the row */
-                const uint32_t src0 = smem_u32(ring + (size_t)slot * kStageBytes) + (uint32_t)(row * kTcRowPitch);
-                for (int k = 0; k < ng; ++k, ++gi) {
-                    if ((gi & 1u) != team) continue;
-                    const uint32_t ab = gi % nabufs;
-                    /* the buffer was last read by the MMAs of group gi - nabufs */
-                    if (gi >= nabufs && !mbar_wait<32>(&sm->done[(gi - nabufs) % kTcAccBufs], ((gi - nabufs) / kTcAccBufs) & 1u, &sm->abort_flag)) {
-                        tc_give_up(sm, P.status, ST_TC_A_EMPTY);
-                        ok = false;
+                if ((it & 1u) == team) {
+                    ok = tc_warp_wait(&sm->full[slot], round & 1u, &sm->abort_flag, lane); /* tcgen05.st is warp-wide: the warp goes on together or not at all */
+                    if (!ok) {
+                        if (lane == 0) tc_give_up(sm, P.status, ST_TC_STAGE_FULL);
                         break;
                     }
-                    const uint32_t dst0 = smem_u32(abuf + (size_t)ab * kTcABytes) + a_off;
-                    if (lane == 0 && (cw % kTcTeamWarps) == 0) tc_stamp(P, 1, gi);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const uint4 wv = lds16_at(src0 + (uint32_t)((((k << 2) + q) ^ (row & 7)) << 4));
-                        const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const uint32_t w = words[c];
-                            const int j = q * 4 + c; /* 16-byte piece (8 values of K) within the group */
-                            sts128(dst0 + (uint32_t)((j >> 3) * kTcKBlockBytes + (((j & 7) ^ (row & 7)) << 4)),
-                                   tc_codes(w), tc_codes(w >> 4), tc_codes(w >> 8), tc_codes(w >> 12));
+                    /* 128-byte swizzle: 16-byte piece c of row r sits at piece c ^ (r & 7) of the row */
+                    const uint32_t src0 = smem_u32(ring + (size_t)slot * kStageBytes) + (uint32_t)(row * kTcRowPitch);
+                    for (int k = 0; k < ng; ++k) {
+                        const uint32_t gk = gi + (uint32_t)k, ab = gk % kTcABufs;
+                        /* the buffer was last read by the MMAs of group gk - 4, whose `done` barrier is this group's too */
+                        if (gk >= (uint32_t)kTcABufs) {
+                            ok = tc_warp_wait(&sm->done[ab], (gk / kTcABufs - 1) & 1u, &sm->abort_flag, lane);
+                            if (!ok) {
+                                if (lane == 0) tc_give_up(sm, P.status, ST_TC_A_EMPTY);
+                                break;
+                            }
+                            tc_fence_after();
                         }
+                        if (stamps) tc_stamp(P, 1, gk);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint4 wv = lds16_at(src0 + (uint32_t)((((k << 2) + q) ^ (row & 7)) << 4));
+                            const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+                            uint32_t v[16];
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const uint32_t w = words[c];
+                                v[4 * c + 0] = tc_codes(w); v[4 * c + 1] = tc_codes(w >> 4);
+                                v[4 * c + 2] = tc_codes(w >> 8); v[4 * c + 3] = tc_codes(w >> 12);
+                            }
+                            tmem_st16(a_lane + ab * (uint32_t)kTcACols + (uint32_t)(q * 16), v);
+                        }
+                        tmem_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&sm->a_ready[ab]);
+                        if (stamps) tc_stamp(P, 2, gk);
                     }
-                    fence_async_smem(); /* the tensor core reads shared memory through the async proxy */
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&sm->a_ready[ab]);
-                    if (lane == 0 && (cw % kTcTeamWarps) == 0) tc_stamp(P, 2, gi);
+                    if (!ok) break;
+                    if (lane == 0) mbar_arrive(&sm->empty[slot]); /* this warp is done with the stage's packed rows */
                 }
-                if (!ok) break;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm->empty[slot]); /* this warp is done with the stage's packed rows */
+                gi += (uint32_t)ng;
+                ++it;
+                if (++slot == nstages) { slot = 0; ++round; }
             }
         }
     } else if (warp >= kTcFirstMmaWarp) {
@@ -367,9 +398,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) ffn_tc_kernel(const __grid_cons
         const uint32_t mine = (uint32_t)(warp - kTcFirstMmaWarp);
         if (lane == 0) {
             const uint32_t idesc = tc_instr_desc(NPAD);
-            const uint64_t adesc0 = tc_smem_desc(smem_u32(abuf), 1024);
             const uint64_t bdesc0 = tc_smem_desc(smem_u32(ring) + kTcRows * kTcRowPitch, 1024);
-            const uint32_t dcol = tmem + mine * (uint32_t)NPAD;
+            const uint32_t dcol = tmem + mine * (uint32_t)NPAD, acol = tmem + (uint32_t)kTcAFirstCol + mine * (uint32_t)kTcACols;
             uint32_t it = 0, gi = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < P.units && ok; u += gridDim.x) {
@@ -379,31 +409,29 @@ __global__ void __launch_bounds__(kTcThreads, 1) ffn_tc_kernel(const __grid_cons
                     const uint32_t slot = it % nstages;
                     for (int k = 0; k < ng; ++k, ++gi) {
                         if (gi % kTcAccBufs != mine) continue;
-                        const uint32_t ab = gi % nabufs;
-                        if (!mbar_wait<32>(&sm->full[slot], (it / nstages) & 1u, &sm->abort_flag)) {
+                        if (!mbar_wait<20>(&sm->full[slot], (it / nstages) & 1u, &sm->abort_flag)) {
                             tc_give_up(sm, P.status, ST_TC_STAGE_FULL);
                             ok = false;
                             break;
                         }
-                        if (!mbar_wait<32>(&sm->a_ready[ab], (gi / nabufs) & 1u, &sm->abort_flag)) {
+                        if (!mbar_wait<20>(&sm->a_ready[mine], (gi / kTcABufs) & 1u, &sm->abort_flag)) {
                             tc_give_up(sm, P.status, ST_TC_A_READY);
                             ok = false;
                             break;
                         }
-                        if (gi >= (uint32_t)kTcAccBufs && !mbar_wait<32>(&sm->d_empty[mine], (gi / kTcAccBufs - 1) & 1u, &sm->abort_flag)) {
+                        if (gi >= (uint32_t)kTcAccBufs && !mbar_wait<20>(&sm->d_empty[mine], (gi / kTcAccBufs - 1) & 1u, &sm->abort_flag)) {
                             tc_give_up(sm, P.status, ST_TC_D_EMPTY);
                             ok = false;
                             break;
                         }
                         tc_fence_after();
                         tc_stamp(P, 3, gi);
-                        /* descriptors differ from the first buffer's only in the start-address field (bytes / 16) */
-                        const uint64_t adesc = adesc0 + (uint64_t)((ab * (uint32_t)kTcABytes) >> 4);
+                        /* descriptors differ from the first stage's only in the start-address field (bytes / 16) */
                         const uint64_t bdesc = bdesc0 + (uint64_t)((slot * (uint32_t)kStageBytes + (uint32_t)(k * NPAD * 256)) >> 4);
 #pragma unroll
                         for (int i = 0; i < FFN_INT4_GROUP / 16; ++i)
-                            tc_mma(dcol, adesc + (uint64_t)(((i >> 2) * kTcKBlockBytes + (i & 3) * 32) >> 4),
-                                   bdesc + (uint64_t)(((i >> 2) * NPAD * 128 + (i & 3) * 32) >> 4), idesc, i > 0 ? 1u : 0u);
+                            tc_mma_ts(dcol, acol + (uint32_t)(i * 8), /* K = 16 is 8 columns of A */
+                                      bdesc + (uint64_t)(((i >> 2) * NPAD * 128 + (i & 3) * 32) >> 4), idesc, i > 0 ? 1u : 0u);
                         tc_commit(&sm->done[mine]);      /* the sums are in tensor memory and the operand buffer is free */
                         tc_commit(&sm->empty[slot]);     /* this group's half of the stage's activation slice has been read */
                         if (ng < kTcGroupsPerStage) tc_commit(&sm->empty[slot]); /* an odd tail: the arrival of the group that is not there */
@@ -429,32 +457,45 @@ __global__ void __launch_bounds__(kTcThreads, 1) ffn_tc_kernel(const __grid_cons
 #pragma unroll
             for (int c = 0; c < NPAD; ++c) acc[c] = 0.0f;
             ok = __all_sync(~0u, ok && !sm->abort_flag);
-            float sc = bf16_bits_to_f32(__ldg(srow + t.g0));
-            for (int g = t.g0; g < t.g1; ++g, ++gi) {
-                if (!ok) continue;
-                const float sc_next = g + 1 < t.g1 ? bf16_bits_to_f32(__ldg(srow + g + 1)) : 0.0f;
-                const uint32_t db = gi % kTcAccBufs;
-                const bool mine = mbar_wait<32>(&sm->done[db], (gi / kTcAccBufs) & 1u, &sm->abort_flag);
-                ok = __all_sync(~0u, mine); /* tcgen05.ld is warp-wide: the warp goes on together or not at all */
-                if (!ok) {
-                    if (lane == 0) tc_give_up(sm, P.status, ST_TC_D_FULL);
-                    continue;
-                }
-                tc_fence_after();
-                if (L == 0) tc_stamp(P, 5, gi);
+            /* The scales of this row come through shared memory, 64 groups at a time: a global load per
+             * group would put its latency (hundreds of cycles) into every turn of the loop below.  A
+             * thread reads back only what it wrote itself, so no barrier is needed. */
+            for (int gc = t.g0; gc < t.g1; gc += kTcScaleGroups) {
+                const int nc = min(kTcScaleGroups, t.g1 - gc);
+                int j = 0;
+                if ((((size_t)grow * G + gc) & 7) == 0) { /* 16-byte loads of 8 scales while whole ones remain */
+                    for (; j + 8 <= nc; j += 8) {
+                        const uint4 v = __ldg((const uint4 *)(srow + gc + j));
+                        const uint16_t *e = (const uint16_t *)&v;
 #pragma unroll
-                for (int t16 = 0; t16 < NT; ++t16) {
-                    uint32_t d[16];
-                    tmem_ld16(lane_addr + db * (uint32_t)NPAD + (uint32_t)(t16 * 16), d);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) acc[t16 * 16 + c] = fmaf(sc, __uint_as_float(d[c]), acc[t16 * 16 + c]);
+                        for (int q = 0; q < 8; ++q) sc_t[(j + q) * kTcRows + L] = e[q];
+                    }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm->d_empty[db]);
-                if (L == 0) tc_stamp(P, 6, gi);
-                sc = sc_next;
+                for (; j < nc; ++j) sc_t[j * kTcRows + L] = __ldg(srow + gc + j);
+                for (int g = gc; g < gc + nc; ++g, ++gi) {
+                    if (!ok) continue;
+                    const float sc = bf16_bits_to_f32(sc_t[(g - gc) * kTcRows + L]);
+                    const uint32_t db = gi % kTcAccBufs;
+                    ok = tc_warp_wait(&sm->done[db], (gi / kTcAccBufs) & 1u, &sm->abort_flag, lane); /* tcgen05.ld is warp-wide: the warp goes on together or not at all */
+                    if (!ok) {
+                        if (lane == 0) tc_give_up(sm, P.status, ST_TC_D_FULL);
+                        continue;
+                    }
+                    tc_fence_after();
+                    if (L == 0) tc_stamp(P, 5, gi);
+#pragma unroll
+                    for (int t16 = 0; t16 < NT; ++t16) {
+                        uint32_t d[16];
+                        tmem_ld16(lane_addr + db * (uint32_t)NPAD + (uint32_t)(t16 * 16), d);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) acc[t16 * 16 + c] = fmaf(sc, __uint_as_float(d[c]), acc[t16 * 16 + c]);
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sm->d_empty[db]);
+                    if (L == 0) tc_stamp(P, 6, gi);
+                }
             }
             /* every epilogue thread passes the same barriers below whatever happened above */
             if (PAIRS) {
@@ -553,13 +594,14 @@ struct TcScratch {
 };
 static TcScratch g_tc_scratch[64];
 static std::mutex g_tc_mutex; /* guards the table; the scratch itself is shared by every call on the device */
-static int g_tc_enabled = 0; /* measured slower than the mma.sync pair up to 32 tokens: opt-in */
+static int g_tc_mode = 2; /* 0: always, 1: never, 2: where it measured faster than the mma.sync pair - more than 32 tokens */
 
-int tc_set_enabled(int on) {
-    const int old = g_tc_enabled;
-    g_tc_enabled = on != 0;
+int tc_set_mode(int mode) {
+    const int old = g_tc_mode;
+    if (mode >= 0 && mode <= 2) g_tc_mode = mode;
     return old;
 }
+static bool tc_wanted(int tokens) { return g_tc_mode == 0 || (g_tc_mode == 2 && tokens > 32); }
 
 /* The driver's tensor-map encoder, through the runtime (no link against the driver library). */
 static PFN_cuTensorMapEncodeTiled_v12000 tc_encoder() {
@@ -593,19 +635,16 @@ static int tc_weight_map(CUtensorMap *map, const void *w, int rows, int K) {
 }
 
 static int tc_tiles_for(int tokens) { return (tokens + 15) / 16; }
-static int tc_smem_bytes(int nt, int stages, int abufs) {
-    return kTcHeader + abufs * kTcABytes + stages * (kTcRows * kTcRowPitch + kTcGroupsPerStage * nt * 16 * 256);
-}
-/* Depths of the two rings for `nt` 16-token column blocks.  The conversion of group g + abufs waits for
- * the MMAs of group g, so the operand ring is what hides the MMA latency: four buffers where they fit
- * next to two or three packed stages - one per MMA-issuing thread, so every `a_ready` barrier has a
- * single waiter that sees each of its phases in turn.  Token counts whose activation slices leave no
- * room for that (49..64 tokens at 227 KB) are not admitted; the mma.sync pair takes them. */
-static bool tc_depths(int nt, int smem_optin, int *stages, int *abufs) {
-    static const int choice[2][2] = {{3, 4}, {2, 4}};
-    for (const auto &c : choice)
-        if (tc_smem_bytes(nt, c[0], c[1]) <= smem_optin) { *stages = c[0]; *abufs = c[1]; return true; }
-    return false;
+static int tc_stage_bytes(int nt) { return kTcRows * kTcRowPitch + kTcGroupsPerStage * nt * 16 * 256; }
+static int tc_smem_bytes(int nt, int stages) { return kTcHeader + kTcScaleBytes + stages * tc_stage_bytes(nt); }
+/* Depth of the packed ring for `nt` 16-token column blocks: whatever shared memory holds, at most 8.
+ * The ring has to cover the latency of a TMA load (about 1.5 us under load) at the SM's share of the
+ * HBM rate, i.e. some 70 KB of packed rows in flight. */
+static bool tc_depth(int nt, int smem_optin, int *stages) {
+    int n = (smem_optin - kTcHeader - kTcScaleBytes) / tc_stage_bytes(nt);
+    if (n > kTcMaxStages) n = kTcMaxStages;
+    *stages = n;
+    return n >= 2;
 }
 static int tc_splits(int H, int I, int sm_count) {
     const int blocks = H / kTcRows, G = I / FFN_INT4_GROUP;
@@ -617,26 +656,26 @@ static int tc_splits(int H, int I, int sm_count) {
 static bool tc_admits(int tokens, int H, int I, int sm_count, int smem_optin) {
     if (tokens < 1 || tokens > 64 || H <= 0 || I <= 0) return false;
     if (H % kTcRows || I % 64 || H % FFN_INT4_GROUP || I % FFN_INT4_GROUP) return false;
-    int stages, abufs;
-    return tc_depths(tc_tiles_for(tokens), smem_optin, &stages, &abufs) && sm_count >= 1;
+    int stages;
+    return tc_depth(tc_tiles_for(tokens), smem_optin, &stages) && sm_count >= 1;
 }
 
 bool tc_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin, char *out, size_t out_bytes) {
-    if (!g_tc_enabled || !tc_admits(tokens, H, I, sm_count, smem_optin)) return false;
+    if (!tc_wanted(tokens) || !tc_admits(tokens, H, I, sm_count, smem_optin)) return false;
     const int nt = tc_tiles_for(tokens), sp = tc_splits(H, I, sm_count);
-    int stages = 0, abufs = 0;
-    tc_depths(nt, smem_optin, &stages, &abufs);
+    int stages = 0;
+    tc_depth(nt, smem_optin, &stages);
     snprintf(out, out_bytes,
              "kernel=tcgen05_pair token_columns=%d threads=%d smem=%d stages=%d operand_buffers=%d accumulator_buffers=%d "
              "tmem_columns=%d gate_up_units=%d gate_up_ctas=%d down_units=%d down_k_splits=%d",
-             nt * 16, kTcThreads, tc_smem_bytes(nt, stages, abufs), stages, abufs, kTcAccBufs, kTcTmemCols, I / 64,
+             nt * 16, kTcThreads, tc_smem_bytes(nt, stages), stages, kTcABufs, kTcAccBufs, kTcTmemCols, I / 64,
              I / 64 < sm_count ? I / 64 : sm_count, (H / kTcRows) * sp, sp);
     return true;
 }
 
 template <int NT>
 static int tc_launch_pair(const TcParams &A, const TcParams &B, int sm_count, cudaStream_t stream) {
-    const int smem = tc_smem_bytes(NT, A.stages, A.abufs);
+    const int smem = tc_smem_bytes(NT, A.stages);
     FFN_CUDA_TRY(cudaFuncSetAttribute(ffn_tc_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "tcgen05 gate/up: shared-memory opt-in");
     FFN_CUDA_TRY(cudaFuncSetAttribute(ffn_tc_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem), "tcgen05 down: shared-memory opt-in");
     ffn_tc_kernel<NT, true><<<A.units < sm_count ? A.units : sm_count, kTcThreads, smem, stream>>>(A);
@@ -658,7 +697,7 @@ void tc_reset_sync() {
 /* normed bf16 [tokens][H] -> layer_out bf16 [tokens][H]; `act` receives act in natural order. */
 int tc_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                   const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual, unsigned *status) {
-    if (!g_tc_enabled) return FFN_NOT_ADMITTED;
+    if (!tc_wanted(tokens)) return FFN_NOT_ADMITTED;
     int dev = 0, smem_optin = 0, sm_count = 0;
     FFN_CUDA_TRY(cudaGetDevice(&dev), "cudaGetDevice");
     if (dev < 0 || dev >= 64) return fail(FFN_ERR_CONFIG, "device index %d out of range", dev);
@@ -666,6 +705,7 @@ int tc_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *laye
     FFN_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev), "SM count");
     if (!tc_admits(tokens, H, I, sm_count, smem_optin)) return FFN_NOT_ADMITTED;
     if (((uintptr_t)w->gate_up_i4 & 15) || ((uintptr_t)w->down_i4 & 15) || ((uintptr_t)normed & 15)) return FFN_NOT_ADMITTED;
+    if (((uintptr_t)w->gate_up_i4_scales & 15) || ((uintptr_t)w->down_i4_scales & 15)) return FFN_NOT_ADMITTED;
     const size_t counters = 4096;
     if ((size_t)(H / kTcRows) * sizeof(unsigned) > counters) return FFN_NOT_ADMITTED;
     /* layout: [arrival counters 4 KiB | input in tile order | act in tile order | partial sums], sized for 64 tokens */
@@ -692,7 +732,7 @@ int tc_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *laye
     A.xt = xt; A.w = w->gate_up_i4; A.s = (const uint16_t *)w->gate_up_i4_scales;
     A.M = tokens; A.npad = npad; A.N = I; A.K = H; A.up_offset = I;
     A.units = I / 64; A.splits = 1;
-    tc_depths(nt, smem_optin, &A.stages, &A.abufs);
+    tc_depth(nt, smem_optin, &A.stages);
     A.act = (uint16_t *)act; A.act_t = act_t;
     A.tp = 1; A.status = status; A.trace = fused_get_trace();
     TcParams B = {};
@@ -700,7 +740,7 @@ int tc_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *laye
     B.xt = act_t; B.w = w->down_i4; B.s = (const uint16_t *)w->down_i4_scales;
     B.M = tokens; B.npad = npad; B.N = H; B.K = I;
     B.splits = tc_splits(H, I, sm_count); B.units = (H / kTcRows) * B.splits;
-    B.stages = A.stages; B.abufs = A.abufs;
+    B.stages = A.stages;
     B.out = (uint16_t *)layer_out; B.residual = (uint16_t *)residual;
     B.partial = (float *)(sc.base + counters + xt_bytes + at_bytes); B.arrivals = (unsigned *)sc.base;
     B.tp = 1; B.status = status;

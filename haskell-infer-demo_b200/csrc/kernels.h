@@ -144,14 +144,14 @@ int kmajor_prefer_dp4a(int on); /* returns the previous setting */
 bool kmajor_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin, char *out, size_t out_bytes);
 /* ffn_mma.cu: the tensor-core path for 3..64 tokens (two launches: gate/up + SiLU*up, down + reduce). */
 /* ffn_tc.cu: the same contract on tcgen05 tensor cores (accumulators in tensor memory); batched_ffn_launch
- * tries it first and falls back to the mma.sync pair for shapes it does not take.  tc_set_enabled(0)
- * turns it off (A/B measurements, tests); returns the previous setting. */
+ * tries it first and falls back to the mma.sync pair for shapes it does not take.  tc_set_mode: 0 always,
+ * 1 never, 2 (default) for more than 32 tokens, where it measured faster; returns the previous mode. */
 int tc_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                   const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual, unsigned *status);
 int batched_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                        const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual, unsigned *status);
 bool tc_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin, char *out, size_t out_bytes);
-int tc_set_enabled(int on);
+int tc_set_mode(int mode);
 void tc_reset_sync();
 int mma_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                    const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual, unsigned *status);

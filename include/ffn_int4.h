@@ -254,14 +254,14 @@ int ffn_int4_describe_kmajor_plan(int tokens, int hidden, int intermediate, int 
  * opt-in and kept for A/B measurement.  Returns the previous setting. */
 int ffn_int4_set_decode_kernel(int which);
 
-/* Which pair of kernels serves 3..64 tokens per pass: 1 (default) the mma.sync pair; 0 the tcgen05
- * pair (tcgen05.mma, FP32 accumulators in tensor memory, packed INT4 rows brought in by tiled TMA
- * loads and converted to BF16 operand tiles on the SM), falling back to the mma.sync pair for shapes
- * it does not take (hidden size not a multiple of 128, intermediate size not a multiple of 64, more
- * than 48 tokens).  Same arithmetic in both: exact codes times BF16 activations summed in FP32 per
- * 128-wide group, times the group's scale (the reference's tiled kernel,
- * csrc/kernels/gemm_quant.cu:134-147).  The tcgen05 pair measured slower than the mma.sync pair up to
- * 32 tokens on B200, hence opt-in.  Returns the previous setting; any other value queries. */
+/* Which pair of kernels serves 3..64 tokens per pass: 1 the mma.sync pair; 0 the tcgen05 pair
+ * (tcgen05.mma with FP32 accumulators and the converted BF16 operand in tensor memory, packed INT4 rows
+ * brought in by tiled TMA loads), falling back to the mma.sync pair for shapes it does not take (hidden
+ * size not a multiple of 128, intermediate size not a multiple of 64); 2 (default) the tcgen05 pair
+ * for more than 32 tokens, where it measured faster on B200 (165 vs 211 us at 64 tokens on the
+ * 5120 x 17408 layer), and the mma.sync pair below.  Same arithmetic in both: exact codes times BF16
+ * activations summed in FP32 per 128-wide group, times the group's scale (the reference's tiled
+ * kernel, csrc/kernels/gemm_quant.cu:134-147).  Returns the previous setting; any other value queries. */
 int ffn_int4_set_batched_kernel(int which);
 
 /* Overlap of consecutive FFN launches in one stream (default 1, on).  The fused FFN kernel is launched

@@ -55,7 +55,12 @@ def test_headline_shape_uses_all_of_shared_memory():
 @pytest.mark.parametrize("hidden,inter,tp", [(5120, 17408, 1), (5120, 17408, 8), (1024, 3072, 1), (2560, 9728, 2)])
 def test_batched_plan(tokens, hidden, inter, tp):
     local = inter // tp
-    p = plan(tokens, hidden, local)
+    assert plan(tokens, hidden, local)["kernel"] == ("tcgen05_pair" if tokens > 32 else "mma_pair")   # the default choice
+    old = L.load().ffn_int4_set_batched_kernel(1)
+    try:
+        p = plan(tokens, hidden, local)
+    finally:
+        L.load().ffn_int4_set_batched_kernel(old)
     assert p["kernel"] == "mma_pair"
     assert p["token_tiles"] * 8 >= tokens and p["token_tiles"] in (1, 2, 4, 8)
     assert p["smem"] * p["ctas_per_sm"] <= SMEM and p["stages"] >= 2
@@ -65,19 +70,16 @@ def test_batched_plan(tokens, hidden, inter, tp):
     slots = SMS * p["ctas_per_sm"]
     eff = lambda u: u / (-(-u // slots) * slots)
     assert eff(p["down_ctas"]) >= eff(hidden // 128) - 1e-9
-    # the opt-in tcgen05 pair: admitted while four operand buffers fit next to two packed stages
+    # the tcgen05 pair, forced
     old = L.load().ffn_int4_set_batched_kernel(0)
     try:
         p = plan(tokens, hidden, local)
     finally:
         L.load().ffn_int4_set_batched_kernel(old)
-    if tokens > 48:
-        assert p["kernel"] == "mma_pair"
-        return
     assert p["kernel"] == "tcgen05_pair"
     assert p["token_columns"] >= tokens and p["token_columns"] % 16 == 0 and p["token_columns"] <= 64
     assert p["smem"] <= SMEM and p["stages"] >= 2 and p["threads"] == 544 and p["operand_buffers"] == 4
-    assert p["accumulator_buffers"] * p["token_columns"] <= p["tmem_columns"] <= 512
+    assert p["accumulator_buffers"] * p["token_columns"] + p["operand_buffers"] * 64 <= p["tmem_columns"] == 512
     assert p["gate_up_units"] * 64 == local and p["gate_up_ctas"] == min(p["gate_up_units"], SMS)
     assert p["down_units"] == (hidden // 128) * p["down_k_splits"] <= SMS
     assert 1 <= p["down_k_splits"] <= 8 and p["down_k_splits"] * 2 <= max(local // 128, 2)

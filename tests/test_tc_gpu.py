@@ -52,7 +52,7 @@ def plan_text(tokens, hidden, inter):
 def test_batched_pair_matches_oracle(cuda, drawn, batched_kernel, cfg, tokens):
     spec = o.CONFIGS[cfg]
     x, layer, want, act = drawn(cfg, tokens)
-    expect = "kernel=tcgen05_pair" if batched_kernel == "tcgen05" and min(tokens, 64) <= 48 else "kernel=mma_pair"
+    expect = "kernel=tcgen05_pair" if batched_kernel == "tcgen05" else "kernel=mma_pair"
     assert expect in plan_text(tokens, spec["hidden"], spec["inter"])
     mlp = upload_layer(layer, cuda)
     ws = mlp.workspace(tokens)
