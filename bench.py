@@ -272,8 +272,10 @@ def run_ours(args):
     stream = torch.cuda.Stream()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
-    def time_steps(step):
+    def time_steps(step, profiled=False):
         """Warm-up, then K steps captured in one graph; median device time of the replays (ms per K steps)."""
+        if profiled:    # `ncu --profile-from-start off` then lists exactly the launches of this function
+            torch.cuda.cudart().cudaProfilerStart()
         for k in range(max(args.warmup, 3)):
             step(k)
         barrier()
@@ -296,6 +298,8 @@ def run_ours(args):
         if world > 1:
             dist.all_reduce(est, op=dist.ReduceOp.MAX)
         reps, times = int(min(400, max(5, -(-600.0 // max(float(est.item()), 1e-3))))), []
+        if args.profile_range:
+            reps = 2
         for _ in range(reps):
             barrier()
             with torch.cuda.stream(stream):
@@ -305,12 +309,15 @@ def run_ours(args):
             barrier()
             times.append(e0.elapsed_time(e1))
         L.device_status()
+        if profiled:
+            torch.cuda.synchronize()
+            torch.cuda.cudart().cudaProfilerStop()
         return statistics.median(times), reps, graph
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms_total, reps, graph_main = time_steps(make_step(True))
+    ms_total, reps, graph_main = time_steps(make_step(True), profiled=args.profile_range)
     # The same rank's slice with no exchange at all (a TP=1 call on the sliced operands): what the step
     # would cost if communication were free.  exposed communication = step - this.
     ms_alone = None
@@ -559,6 +566,10 @@ def main():
                          "single-launch kernel, which measured faster and is the default")
     ap.add_argument("--batched-kernel", default="", choices=["", "tcgen05", "mma.sync"],
                     help="3..64 tokens: which pair of kernels runs (default: the library's own choice)")
+    ap.add_argument("--profile-range", action="store_true",
+                    help="for a launch list under `ncu --profile-from-start off`: the warm-up and the timed graph replays "
+                         "(two of them instead of about 0.6 s worth) run between cudaProfilerStart and cudaProfilerStop; "
+                         "numbers printed by such a run are not bench values")
     ap.add_argument("--no-overlap", action="store_true",
                     help="comparison variant: launch without the programmatic-dependent-launch attribute")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],

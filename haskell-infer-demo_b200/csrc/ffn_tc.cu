@@ -217,7 +217,13 @@ __device__ __forceinline__ TcUnit tc_unit(const TcParams &P, int u) {
     } else {
         t.rb = u / P.splits; t.sp = u % P.splits;
         t.row_a = t.rb * kTcRows; t.row_b = t.row_a + 64;
+        /* split boundaries on multiples of 8 groups where the split is long enough: the epilogue then
+         * fetches its row's scales with 16-byte loads */
         t.g0 = (int)((long long)G * t.sp / P.splits); t.g1 = (int)((long long)G * (t.sp + 1) / P.splits);
+        if (G >= 16 * P.splits) {
+            if (t.sp > 0) t.g0 = (t.g0 + 4) & ~7;
+            if (t.sp + 1 < P.splits) t.g1 = (t.g1 + 4) & ~7;
+        }
     }
     return t;
 }
@@ -471,6 +477,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) ffn_tc_kernel(const __grid_cons
                         for (int q = 0; q < 8; ++q) sc_t[(j + q) * kTcRows + L] = e[q];
                     }
                 }
+#pragma unroll 8
                 for (; j < nc; ++j) sc_t[j * kTcRows + L] = __ldg(srow + gc + j);
                 for (int g = gc; g < gc + nc; ++g, ++gi) {
                     if (!ok) continue;
