@@ -551,6 +551,67 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------
+# the other decode GEMVs of the format (single-matrix mode of the streaming kernel)
+# ------------------------------------------------------------------------------------------------
+def run_gemv(args):
+    """`--gemv N,K`: device time of one INT4 GEMV/GEMM call (ffn_gemm_int4_bf16, M = --tokens) on an [N, K]
+    matrix - attention projections, the LM head - rotating through weight copies larger than 2x L2.
+    One JSON line; a side measurement, not the headline metric."""
+    import ctypes
+    import torch
+    from haskell_infer_demo_b200 import lib as L
+    n, k = (int(v) for v in args.gemv.split(","))
+    m = args.tokens
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    lib = L.load()
+    bytes_per = n * k // 2 + n * (k // 128) * 2
+    copies = max(2, int(2.2 * L2_BYTES / bytes_per) + 1)
+    ws = [(torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev) & 0x77,
+           torch.full((n, k // 128), 0.01, dtype=torch.bfloat16, device=dev)) for _ in range(copies)]
+    x = torch.randn((m, k), device=dev).to(torch.bfloat16)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.Stream()
+
+    def call(c):
+        p, sc = ws[c % copies]
+        L.check(lib.ffn_gemm_int4_bf16(x.data_ptr(), p.data_ptr(), sc.data_ptr(), out.data_ptr(), m, n, k, 128,
+                                       ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    with torch.cuda.stream(stream):
+        for c in range(max(args.warmup, 3)):
+            call(c)
+    torch.cuda.synchronize()
+    L.device_status()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for c in range(args.steps):
+                call(c)
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1, ts = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True), []
+    for _ in range(20):
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3 / args.steps)
+    L.device_status()
+    us = statistics.median(ts)
+    peak, peak_kind = measured_peak_gbs()
+    plan = ctypes.create_string_buffer(1024)
+    lib.ffn_int4_describe_gemm_plan(m, n, k, 148, 232448, plan, 1024)
+    print(json.dumps({"metric": "int4_gemm_latency", "value": round(us, 3), "unit": "us/call", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "higher_is_better": False, "dtype": "int4 weights x bf16 activations, fp32 accumulate",
+                      "data": "synthetic", "config": {"workload": f"INT4 GEMM M={m} N={n} K={k}", "l2": f"rotating {copies} copies",
+                                                     "plan": plan.value.decode()},
+                      "roofline": {"bound": "hbm", "achieved": round(bytes_per / us / 1e3, 1), "peak": peak, "unit": "GB/s",
+                                   "frac": round(bytes_per / us / 1e3 / peak, 4), "peak_source": peak_kind},
+                      "gpu_launches": args.steps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -579,8 +640,11 @@ def main():
     ap.add_argument("--layers", type=int, default=0,
                     help="0: one FFN per step (the headline workload).  L > 0: a step is one pass of h <- h + "
                          "FFN_l(RMSNorm_l(h)) through L independent layers (BASELINE configs[4] at L=64)")
+    ap.add_argument("--gemv", default="", help="N,K: time one INT4 GEMM call of that shape instead of the FFN (side measurement)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.gemv:
+        run_gemv(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

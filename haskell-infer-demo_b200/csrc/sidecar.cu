@@ -671,7 +671,7 @@ static int load_ranks(const char *dir, int num_layers, int hidden, int inter, in
             slice_into(d_p.data(), down_p.data(), down.k / 2, 0, down.n, dv[2] / 2, drow_b);
             slice_into(d_s.data(), down_s.data(), down.k / down.group * 2, 0, down.n, dv[2] / down.group * 2, dsrow_b);
 
-            if (cudaSetDevice(devices[i]) != cudaSuccess) { status = fail(FFN_ERR_CUDA, "ffn_load_quantized_ffn: cannot select device %d", devices[i]); break; }
+            if (cudaSetDevice(devices[i]) != cudaSuccess) { status = fail(FFN_ERR_CUDA, "ffn_quantized_ffn_prepare_decode: cannot select device %d", devices[i]); break; }
             Staging &st = staging[i];
             const size_t need = gu_p.size() + gu_s.size() + d_p.size() + d_s.size() + 4 * 256;
             if (!st.buf[0]) {
@@ -797,13 +797,13 @@ int ffn_shard_view(int rule, long long rows, long long cols, int tp, int rank, l
     return shard_view(rule, rows, cols, tp, rank, view4);
 }
 
-/* Registers the k-major copy of every loaded layer's down projection (the decode kernels of one and
- * two tokens use it, see ffn_decode_layer_prepare).  All or nothing, like the load itself. */
+/* Registers the k-major copy of every loaded layer's down projection (see ffn_decode_layer_prepare).
+ * All or nothing. */
 static int prepare_loaded(QuantizedFfn *q) {
     int restore = 0;
     (void)cudaGetDevice(&restore);
     int st = FFN_OK;
-    if (cudaSetDevice(q->device) != cudaSuccess) st = fail(FFN_ERR_CUDA, "ffn_load_quantized_ffn: cannot select device %d", q->device);
+    if (cudaSetDevice(q->device) != cudaSuccess) st = fail(FFN_ERR_CUDA, "ffn_quantized_ffn_prepare_decode: cannot select device %d", q->device);
     FfnModelDims dims = {};
     dims.hidden_size = q->hidden;
     dims.intermediate_size = q->inter_local;
@@ -814,7 +814,7 @@ static int prepare_loaded(QuantizedFfn *q) {
         w.i4_group = FFN_INT4_GROUP;
         st = ffn_decode_layer_prepare(&w, &dims, nullptr);
     }
-    if (st == FFN_OK && cudaDeviceSynchronize() != cudaSuccess) st = fail(FFN_ERR_CUDA, "ffn_load_quantized_ffn: building the k-major copies failed");
+    if (st == FFN_OK && cudaDeviceSynchronize() != cudaSuccess) st = fail(FFN_ERR_CUDA, "ffn_quantized_ffn_prepare_decode: building the k-major copies failed");
     (void)cudaSetDevice(restore);
     return st;
 }
@@ -827,9 +827,14 @@ int ffn_load_quantized_ffn(const char *manifest_dir, int num_layers, int hidden,
     FFN_CUDA_TRY(cudaGetDevice(&dev), "ffn_load_quantized_ffn: no CUDA device");
     QuantizedFfn *q = nullptr;
     int st = load_ranks(manifest_dir, num_layers, hidden, intermediate, tp < 1 ? 1 : tp, &rank, &dev, 1, &q);
-    if (st == FFN_OK && (st = prepare_loaded(q)) != FFN_OK) { delete q; q = nullptr; }
     if (st == FFN_OK) *out = (FfnQuantizedFfn *)q;
     return st;
+}
+
+int ffn_quantized_ffn_prepare_decode(FfnQuantizedFfn *handle) {
+    clear_error();
+    if (!handle) return fail(FFN_ERR_CONFIG, "ffn_quantized_ffn_prepare_decode: null handle");
+    return prepare_loaded((QuantizedFfn *)handle);
 }
 
 int ffn_load_quantized_ffn_ranks(const char *manifest_dir, int num_layers, int hidden, int intermediate, int tp,
@@ -840,7 +845,6 @@ int ffn_load_quantized_ffn_ranks(const char *manifest_dir, int num_layers, int h
     QuantizedFfn *q[16] = {};
     for (int i = 0; i < tp; ++i) ranks[i] = i;
     int st = load_ranks(manifest_dir, num_layers, hidden, intermediate, tp, ranks, devices, tp, q);
-    for (int i = 0; i < tp && st == FFN_OK; ++i) st = prepare_loaded(q[i]);
     if (st != FFN_OK) {
         for (int i = 0; i < tp; ++i) delete q[i];
         return st;

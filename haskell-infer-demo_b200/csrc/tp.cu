@@ -291,6 +291,13 @@ int ffn_allreduce_sum(FfnTpComm *const *comms, void *const *streams, int count, 
     return st;
 }
 
+/* The input of a host-buffer call, fetched from mapped host memory by one small CTA: a few
+ * microseconds of PCIe reads in flight together, where a copy-engine transfer costs its own start-up
+ * and a hand-over between the copy engine and the compute queue. */
+__global__ void stage_host_input_kernel(uint4 *__restrict__ dst, const uint4 *__restrict__ src_mapped, int chunks) {
+    for (int i = threadIdx.x; i < chunks; i += blockDim.x) dst[i] = src_mapped[i];
+}
+
 int ffn_forward_mlp_host(FfnTpComm *comm, void *stream, const void *normed_host, void *layer_out_host, void *staging,
                          void *ws, const FfnMlpWeights *w, int tokens, const FfnModelDims *dims) {
     clear_error();
@@ -314,7 +321,13 @@ int ffn_forward_mlp_host(FfnTpComm *comm, void *stream, const void *normed_host,
      * by the CTAs that own its rows, and can go straight to mapped host memory. */
     uint16_t *x_dev = (uint16_t *)staging, *y_dev = (uint16_t *)mapped(layer_out_host);
     const bool stage_out = y_dev == nullptr;
-    FFN_CUDA_TRY(cudaMemcpyAsync(x_dev, normed_host, bytes, cudaMemcpyDefault, s), "ffn_forward_mlp_host: input copy");
+    const void *x_mapped = mapped(normed_host);
+    if (x_mapped && bytes <= (64u << 10) && !(((uintptr_t)x_mapped | (uintptr_t)x_dev) & 15)) {
+        stage_host_input_kernel<<<1, 512, 0, s>>>((uint4 *)x_dev, (const uint4 *)x_mapped, (int)(bytes / 16));
+        FFN_CUDA_TRY(cudaGetLastError(), "ffn_forward_mlp_host: input staging launch");
+    } else {
+        FFN_CUDA_TRY(cudaMemcpyAsync(x_dev, normed_host, bytes, cudaMemcpyDefault, s), "ffn_forward_mlp_host: input copy");
+    }
     if (stage_out) y_dev = (uint16_t *)staging + (size_t)tokens * dims->hidden_size;
     TpComm *c = (TpComm *)comm;
     const int st = (c && c->tp > 1) ? ffn_forward_mlp_tp(comm, stream, x_dev, ws, y_dev, w, tokens, dims, nullptr)

@@ -82,6 +82,7 @@ def _declare(lib):
         "ffn_load_quantized_ffn_ranks": [ctypes.c_char_p, ci, ci, ci, ci, ctypes.POINTER(ci), ctypes.POINTER(vp)],
         "ffn_quantized_ffn_layer": [vp, ci, ctypes.POINTER(MlpWeights)],
         "ffn_quantized_ffn_free": [vp],
+        "ffn_quantized_ffn_prepare_decode": [vp],
         "test_gemm_int4": [vp, vp, vp, vp, ci, ci, ci, ci],
         "test_silu_mul_packed": [vp, vp, ci, ci],
         "test_norm": [vp, vp, vp, ci, ci],

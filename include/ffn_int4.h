@@ -229,13 +229,16 @@ int ffn_forward_mlp_prepared(void *cublas, void *stream, const void *normed, voi
  * w->down_i4 / w->down_i4_scales ([H][I/2], [H][I/128]; dims->intermediate_size is the rank-local I).
  * With it every CTA multiplies the down projection against only the act values it computed itself,
  * so the kernel needs no grid-wide hand-over between the two projections, and ffn_decode_stack runs
- * the whole stack in one persistent launch per 64 layers.  Results are not bit-identical to the
- * row-major kernel's (other summation order; same bars against the oracle).  The copy costs H*I/2 +
+ * the whole stack in one persistent launch per 64 layers.  On B200 this kernel MEASURED SLOWER than
+ * the row-major one (37.6 against 30.3 us on the 5120 x 17408 layer, 2628 against 2141 us for 64
+ * layers), so preparing a layer is an opt-in for experiments, not a recommendation.  Results are not
+ * bit-identical to the row-major kernel's (other summation order; same bars against the oracle).  The copy costs H*I/2 +
  * H*I/64 bytes of device memory per layer (+33 % of a layer's INT4 bytes) and is found again by the
  * ADDRESS w->down_i4: ffn_forward_mlp*, ffn_forward_mlp_tp, ffn_forward_mlp_host and ffn_decode_stack
  * use it whenever the layer they are given has one.  Call again after overwriting the weights, and
  * ffn_decode_layer_release before freeing them (a stale copy would be used for whatever is put at that
- * address next).  ffn_load_quantized_ffn[_ranks] registers its layers itself.  Layers without a copy
+ * address next).  ffn_quantized_ffn_prepare_decode does it for every layer of a loaded handle (and the
+ * handle's free releases them).  Layers without a copy
  * take the row-major kernel, which reads the reference's own uploads (csrc/engine.cu:2361-2401)
  * unchanged.  No counterpart in the reference. */
 int ffn_decode_layer_prepare(const FfnMlpWeights *w, const FfnModelDims *dims, void *stream);
@@ -437,6 +440,9 @@ int ffn_load_quantized_ffn_ranks(const char *manifest_dir, int num_layers, int h
 /* Fills the INT4 members of `w` (gate_up_i4, its scales, down_i4, its scales, i4_group) with the
  * layer's device pointers, which stay owned by the handle (LayerWeights::owned, csrc/engine.cu:2184). */
 int ffn_quantized_ffn_layer(const FfnQuantizedFfn *handle, int layer, FfnMlpWeights *w);
+/* ffn_decode_layer_prepare for every layer of the handle, on the handle's device (opt-in; all or nothing).
+ * No counterpart in the reference. */
+int ffn_quantized_ffn_prepare_decode(FfnQuantizedFfn *handle);
 int ffn_quantized_ffn_free(FfnQuantizedFfn *handle);
 
 /* Replaces the reference's offline converter (scripts/quantize_weights.py:155-325, `convert`): reads the

@@ -116,3 +116,27 @@ def test_refusals(cuda):
     mlp.weights.gate_up_i4 = 0
     with pytest.raises(FfnError, match="no INT4 operands"):
         mlp.forward_mlp_prepared(dev_bf16(x, cuda))
+
+
+@pytest.mark.parametrize("pinned", [True, False], ids=["pinned", "pageable"])
+@pytest.mark.parametrize("tokens", [1, 2, 16])
+def test_forward_mlp_host_matches_oracle(cuda, drawn, tokens, pinned):
+    """The host-buffer entry (input and output in host memory, one call, synchronous): pinned buffers take
+    the mapped paths (input fetched by a staging kernel, output written by the FFN kernel itself),
+    pageable ones the copy calls; either way the result is complete when the call returns."""
+    from haskell_infer_demo_b200.ops import forward_mlp_host
+    x, layer, want = drawn(0, tokens)
+    mlp = upload_layer(layer, cuda)
+    h = o.CONFIGS[0]["hidden"]
+    x_host = torch.from_numpy(o.bf16_bits(x).view(np.int16)).view(torch.bfloat16).clone()
+    y_host = torch.full((tokens, h), float("nan"), dtype=torch.bfloat16)
+    if pinned:
+        x_host, y_host = x_host.pin_memory(), y_host.pin_memory()
+    staging = torch.empty((2 * tokens, h), dtype=torch.bfloat16, device=cuda)
+    ws = mlp.workspace(tokens)
+    for _ in range(3):
+        y_host.fill_(float("nan"))
+        forward_mlp_host(mlp, x_host, y_host, staging, ws)      # no synchronize here: the call is synchronous
+        got = y_host.float().numpy().copy()
+        assert_ffn_close(got, want, f"host entry, {'pinned' if pinned else 'pageable'}, M={tokens}")
+    L.device_status()

@@ -55,7 +55,7 @@ def test_load_slices_and_runs(cuda, tmp_path, tp):
             assert np.array_equal(device_bytes(w.gate_up_i4_scales, gs.size * 2), gs.ravel().view(np.uint8))
             assert np.array_equal(device_bytes(w.down_i4, dp.size), dp.ravel())
             assert np.array_equal(device_bytes(w.down_i4_scales, ds.size * 2), ds.ravel().view(np.uint8))
-            assert lib.ffn_decode_layer_is_prepared(ctypes.byref(w)) == 1      # the loader registers the k-major copies
+            assert lib.ffn_decode_layer_is_prepared(ctypes.byref(w)) == 0      # k-major copies are an opt-in (below)
             if tp == 1:
                 # run the FFN straight from the loaded operands
                 dims = L.ModelDims()
@@ -67,6 +67,17 @@ def test_load_slices_and_runs(cuda, tmp_path, tp):
                                                      ctypes.c_void_p(out.data_ptr()), ctypes.byref(w), 1, ctypes.byref(dims)))
                 L.device_status()
                 assert_ffn_close(host_f32(out), o.ffn(layers[l], x), f"layer {l} from the loaded sidecar")
+        if tp == 1:
+            # the opt-in k-major copies for the whole handle: another kernel, the same answer
+            assert lib.ffn_quantized_ffn_prepare_decode(handle) == 0, lib.ffn_int4_last_error()
+            for l in range(nl):
+                w = MlpWeights()
+                assert lib.ffn_quantized_ffn_layer(handle, l, ctypes.byref(w)) == 0
+                assert lib.ffn_decode_layer_is_prepared(ctypes.byref(w)) == 1
+                L.check(lib.ffn_forward_mlp_prepared(None, None, ctypes.c_void_p(xd.data_ptr()), ctypes.c_void_p(ws.data_ptr()),
+                                                     ctypes.c_void_p(out.data_ptr()), ctypes.byref(w), 1, ctypes.byref(dims)))
+                L.device_status()
+                assert_ffn_close(host_f32(out), o.ffn(layers[l], x), f"layer {l} through its k-major copy")
         assert lib.ffn_quantized_ffn_free(handle) == 0
 
 
