@@ -69,7 +69,7 @@ struct FusedParams {
     const uint16_t *norm_w;
     float norm_eps;
     int norm_gemma;
-    long long *trace;     /* optional [kTraceWords] clock64 stamps of CTA 0 (NULL = off) */
+    long long *trace;     /* optional [CTAs][16] global-timer stamps of every CTA's pipeline events (NULL = off) */
     int early_weights;    /* 1: the first fill of every stage is issued before the wait on the previous launch of
                              the stream (set by the host together with the dependent-launch attribute) */
     int gemv;             /* 1: single-matrix mode - only phase 2 runs, its activation is the caller's input
@@ -113,7 +113,11 @@ __device__ __forceinline__ int cta_begin(int total, int cta, int ctas) {
 }
 
 __device__ __forceinline__ void stamp(const FusedParams &P, int slot) {
-    if (P.trace && blockIdx.x == 0) P.trace[slot] = clock64();
+    if (P.trace) { /* every CTA, global timer: [cta][16] */
+        long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        P.trace[blockIdx.x * 16 + slot] = t;
+    }
 }
 
 /* ---- consumer side of one phase ------------------------------------------------------------ */

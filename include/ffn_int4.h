@@ -87,8 +87,10 @@ int ffn_int4_describe_plan(int tokens, int hidden, int intermediate, int sm_coun
 /* The same for one ffn_gemm_int4_bf16 call of m rows against an [n][k] matrix. */
 int ffn_int4_describe_gemm_plan(int m, int n, int k, int sm_count, int smem_optin, char *out, size_t out_bytes);
 
-/* Debugging aid: when given a device buffer of 16 int64, CTA 0 of every later fused launch writes
- * clock64() stamps of its pipeline events there (NULL switches it off).  No counterpart in the
+/* Debugging aid: when given a device buffer of 16 int64 per SM (16 x 148 on B200), every CTA of every
+ * later decode-kernel launch writes global-timer stamps (ns) of its pipeline events to its own 16
+ * words; the tcgen05 pair's gate/up launch instead has CTA 0 write SM-clock stamps of its roles' first
+ * 32 groups to words [role * 32 + group] (NULL switches it off).  No counterpart in the
  * reference (its profiler times whole regions with events, csrc/profile.cu:114-144). */
 void ffn_int4_debug_trace(void *device_buffer);
 
