@@ -601,14 +601,19 @@ struct TcScratch {
 };
 static TcScratch g_tc_scratch[64];
 static std::mutex g_tc_mutex; /* guards the table; the scratch itself is shared by every call on the device */
-static int g_tc_mode = 2; /* 0: always, 1: never, 2: where it measured faster than the mma.sync pair - more than 32 tokens */
+static int g_tc_mode = 2; /* 0: always, 1: never, 2: where it measured faster than the mma.sync pair (tc_wanted) */
 
 int tc_set_mode(int mode) {
     const int old = g_tc_mode;
     if (mode >= 0 && mode <= 2) g_tc_mode = mode;
     return old;
 }
-static bool tc_wanted(int tokens) { return g_tc_mode == 0 || (g_tc_mode == 2 && tokens > 32); }
+/* Measured on B200 (5120 x 17408): faster than the mma.sync pair above 32 tokens when the gate/up launch
+ * has more units than SMs (165 vs 210 us at 64 tokens); a tie on tensor-parallel slices (150 vs 150 us
+ * at TP=2, 138 vs 137 at TP=4), which therefore stay with the mma.sync pair. */
+static bool tc_wanted(int tokens, int I, int sm_count) {
+    return g_tc_mode == 0 || (g_tc_mode == 2 && tokens > 32 && I / 64 > sm_count);
+}
 
 /* The driver's tensor-map encoder, through the runtime (no link against the driver library). */
 static PFN_cuTensorMapEncodeTiled_v12000 tc_encoder() {
@@ -668,7 +673,7 @@ static bool tc_admits(int tokens, int H, int I, int sm_count, int smem_optin) {
 }
 
 bool tc_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin, char *out, size_t out_bytes) {
-    if (!tc_wanted(tokens) || !tc_admits(tokens, H, I, sm_count, smem_optin)) return false;
+    if (!tc_wanted(tokens, I, sm_count) || !tc_admits(tokens, H, I, sm_count, smem_optin)) return false;
     const int nt = tc_tiles_for(tokens), sp = tc_splits(H, I, sm_count);
     int stages = 0;
     tc_depth(nt, smem_optin, &stages);
@@ -704,13 +709,12 @@ void tc_reset_sync() {
 /* normed bf16 [tokens][H] -> layer_out bf16 [tokens][H]; `act` receives act in natural order. */
 int tc_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                   const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual, unsigned *status) {
-    if (!tc_wanted(tokens)) return FFN_NOT_ADMITTED;
     int dev = 0, smem_optin = 0, sm_count = 0;
     FFN_CUDA_TRY(cudaGetDevice(&dev), "cudaGetDevice");
     if (dev < 0 || dev >= 64) return fail(FFN_ERR_CONFIG, "device index %d out of range", dev);
     FFN_CUDA_TRY(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev), "smem opt-in");
     FFN_CUDA_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev), "SM count");
-    if (!tc_admits(tokens, H, I, sm_count, smem_optin)) return FFN_NOT_ADMITTED;
+    if (!tc_wanted(tokens, I, sm_count) || !tc_admits(tokens, H, I, sm_count, smem_optin)) return FFN_NOT_ADMITTED;
     if (((uintptr_t)w->gate_up_i4 & 15) || ((uintptr_t)w->down_i4 & 15) || ((uintptr_t)normed & 15)) return FFN_NOT_ADMITTED;
     if (((uintptr_t)w->gate_up_i4_scales & 15) || ((uintptr_t)w->down_i4_scales & 15)) return FFN_NOT_ADMITTED;
     const size_t counters = 4096;

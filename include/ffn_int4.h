@@ -263,8 +263,9 @@ int ffn_int4_set_decode_kernel(int which);
  * (tcgen05.mma with FP32 accumulators and the converted BF16 operand in tensor memory, packed INT4 rows
  * brought in by tiled TMA loads), falling back to the mma.sync pair for shapes it does not take (hidden
  * size not a multiple of 128, intermediate size not a multiple of 64); 2 (default) the tcgen05 pair
- * for more than 32 tokens, where it measured faster on B200 (165 vs 211 us at 64 tokens on the
- * 5120 x 17408 layer), and the mma.sync pair below.  Same arithmetic in both: exact codes times BF16
+ * where it measured faster on B200 - more than 32 tokens and more gate/up units (intermediate size / 64)
+ * than SMs: 165 vs 211 us at 64 tokens on the 5120 x 17408 layer - and the mma.sync pair elsewhere
+ * (tensor-parallel slices measured a tie).  Same arithmetic in both: exact codes times BF16
  * activations summed in FP32 per 128-wide group, times the group's scale (the reference's tiled
  * kernel, csrc/kernels/gemm_quant.cu:134-147).  Returns the previous setting; any other value queries. */
 int ffn_int4_set_batched_kernel(int which);
