@@ -472,7 +472,8 @@ __global__ void __launch_bounds__(kThreads, 1) ffn_fused_kernel(const FusedParam
         if (!P.gemv) {
             ok = epilogue_phase<MT, true>(P, P.p1, sm, 0, seq);
             /* arrive at the grid barrier: the act rows of this CTA are stored */
-            __threadfence(); /* every lane publishes its own act stores */
+            /* The lanes' act stores are ordered before lane 0's release by the warp barrier (release is
+             * cumulative over it), so no lane needs a fence of its own. */
             __syncwarp();
             if (lane == 0) {
                 asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.sync + 0) : "memory");
