@@ -4,7 +4,10 @@
  *
  * Structure and hand-over protocol are those of ffn_kmajor.cu (k-major copy of the down projection,
  * every CTA multiplies the down projection against the act values it produced itself, partial sums and
- * the residual stream travel as tagged words).  What changes is the consumers' arithmetic.  With
+ * the residual stream travel as tagged words).  What changes is the consumers' arithmetic.  OPT-IN
+ * (ffn_int4_set_decode_kernel(0)): on B200 this variant measured slower than the dp4a kernels (54.7 us
+ * against 40.6 / 30.3 us per 5120 x 17408 layer - the legacy mma.sync integer path is slow there) and its
+ * 15-bit planes with one exponent per 128 values are coarser than their 16 bits per 32.  The idea: with
  * dp4a a thread spends 7..10 instructions per 8 codes, and 17 warps of such work keep pace with the
  * HBM stream only barely: every stall of the pipeline is lost time.  Here a 4-bit code is still
  * widened to the signed byte 16*code with one logic operation per four codes, but the products are
