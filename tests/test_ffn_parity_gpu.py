@@ -124,7 +124,7 @@ def test_forward_mlp_host_matches_oracle(cuda, drawn, tokens, pinned):
     """The host-buffer entry (input and output in host memory, one call, synchronous): pinned buffers take
     the mapped paths (input fetched by a staging kernel, output written by the FFN kernel itself),
     pageable ones the copy calls; either way the result is complete when the call returns."""
-    from haskell_infer_demo_b200.ops import forward_mlp_host
+    from haskell_infer_demo_b200.ops import bind_forward_mlp_host, forward_mlp_host
     x, layer, want = drawn(0, tokens)
     mlp = upload_layer(layer, cuda)
     h = o.CONFIGS[0]["hidden"]
@@ -139,4 +139,8 @@ def test_forward_mlp_host_matches_oracle(cuda, drawn, tokens, pinned):
         forward_mlp_host(mlp, x_host, y_host, staging, ws)      # no synchronize here: the call is synchronous
         got = y_host.float().numpy().copy()
         assert_ffn_close(got, want, f"host entry, {'pinned' if pinned else 'pageable'}, M={tokens}")
+    call = bind_forward_mlp_host(mlp, x_host, y_host, staging, ws)   # the same call with its arguments converted once
+    y_host.fill_(float("nan"))
+    call()
+    assert np.array_equal(y_host.view(torch.int16).numpy(), o.bf16_bits(got).view(np.int16))
     L.device_status()
