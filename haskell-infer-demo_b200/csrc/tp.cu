@@ -295,6 +295,9 @@ int ffn_allreduce_sum(FfnTpComm *const *comms, void *const *streams, int count, 
  * microseconds of PCIe reads in flight together, where a copy-engine transfer costs its own start-up
  * and a hand-over between the copy engine and the compute queue. */
 __global__ void stage_host_input_kernel(uint4 *__restrict__ dst, const uint4 *__restrict__ src_mapped, int chunks) {
+    /* The FFN kernel that follows is launched with the dependent-launch attribute: let it start now
+     * (barrier set-up, first weight copies); it waits for this grid before it reads the input. */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     for (int i = threadIdx.x; i < chunks; i += blockDim.x) dst[i] = src_mapped[i];
 }
 
