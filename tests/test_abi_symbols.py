@@ -148,3 +148,16 @@ def test_header_conforms_to_the_reference_headers_where_a_checkout_exists():
     proc = subprocess.run(["make", "-C", os.path.join(ROOT, "oracle"), f"REFERENCE={ref}", "_ref/abi_conformance.o"],
                           capture_output=True, text=True)
     assert proc.returncode == 0 and os.path.exists(obj), proc.stdout + proc.stderr
+
+
+def test_kernel_switches_query_set_and_restore_without_a_gpu():
+    """The A/B switches are plain host state: a value outside their range queries, a set returns the
+    previous setting, and the defaults are the measured-faster kernels."""
+    lib = L.load()
+    for name, default, other in (("ffn_int4_set_decode_kernel", 1, 0), ("ffn_int4_set_batched_kernel", 2, 1),
+                                 ("ffn_int4_set_launch_overlap", 1, 0)):
+        fn = getattr(lib, name)
+        assert fn(-1) == default, name
+        assert fn(other) == default and fn(-1) == other, name
+        assert fn(default) == other and fn(-1) == default, name
+    assert lib.ffn_quantized_ffn_prepare_decode(None) == -4 and b"null handle" in lib.ffn_int4_last_error()
