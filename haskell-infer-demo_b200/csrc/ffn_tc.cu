@@ -67,7 +67,7 @@ constexpr int kTcACols = FFN_INT4_GROUP / 2;  /* 64 columns of tensor memory hol
 constexpr int kTcAFirstCol = 256;             /* columns 0..255: 4 accumulators of up to 64 FP32 columns; 256..511: 4 operand buffers */
 constexpr int kTcTmemCols = 512;
 constexpr int kTcEpiWarps = 4, kTcConvWarps = 8, kTcMmaWarps = 4;
-constexpr int kTcConvTeams = 2;               /* conversion teams of 4 warps: team t converts the groups with index = t mod 2 */
+constexpr int kTcConvTeams = 2;               /* conversion teams of 4 warps: team t converts the stages with index = t mod 2 */
 constexpr int kTcTeamWarps = kTcConvWarps / kTcConvTeams;
 constexpr int kTcProducerWarp = kTcEpiWarps, kTcFirstConvWarp = kTcEpiWarps + 1, kTcFirstMmaWarp = kTcFirstConvWarp + kTcConvWarps;
 constexpr int kTcThreads = (kTcFirstMmaWarp + kTcMmaWarps) * 32;        /* 544 */
@@ -96,7 +96,6 @@ static_assert(sizeof(TcSmem) <= kTcHeader, "header");
 struct TcParams {
     CUtensorMap wmap;         /* the packed rows [rows][K/2] as a 2-D byte tensor, box 128 bytes x 64 rows, 128-byte swizzle */
     const uint8_t *xt;        /* activations in tile order */
-    const uint8_t *w;         /* packed rows [rows][K/2] */
     const uint16_t *s;        /* scales [rows][K/128] */
     int M, npad;              /* tokens; tokens padded to a multiple of 16 */
     int N, K;                 /* pairs launch: gate/up pairs of this rank; down launch: output rows.  K: columns */
@@ -740,7 +739,7 @@ int tc_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *laye
     TcParams A = {};
     int st = tc_weight_map(&A.wmap, w->gate_up_i4, 2 * I, H);
     if (st) return st;
-    A.xt = xt; A.w = w->gate_up_i4; A.s = (const uint16_t *)w->gate_up_i4_scales;
+    A.xt = xt; A.s = (const uint16_t *)w->gate_up_i4_scales;
     A.M = tokens; A.npad = npad; A.N = I; A.K = H; A.up_offset = I;
     A.units = I / 64; A.splits = 1;
     tc_depth(nt, smem_optin, &A.stages);
@@ -748,7 +747,7 @@ int tc_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *laye
     A.tp = 1; A.status = status; A.trace = fused_get_trace();
     TcParams B = {};
     if ((st = tc_weight_map(&B.wmap, w->down_i4, H, I))) return st;
-    B.xt = act_t; B.w = w->down_i4; B.s = (const uint16_t *)w->down_i4_scales;
+    B.xt = act_t; B.s = (const uint16_t *)w->down_i4_scales;
     B.M = tokens; B.npad = npad; B.N = H; B.K = I;
     B.splits = tc_splits(H, I, sm_count); B.units = (H / kTcRows) * B.splits;
     B.stages = A.stages;
