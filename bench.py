@@ -412,7 +412,7 @@ def run_ours(args):
             "kernel": ("persistent decode kernel over k-major down projections (dp4a)" if kmajor else
                        "row-major single-launch kernel (dp4a)" if m <= 2 else
                        "batched pair (tcgen05, accumulators and converted operand in tensor memory)"
-                       if L.load().ffn_int4_set_batched_kernel(-1) == 0 or (L.load().ffn_int4_set_batched_kernel(-1) == 2 and m > 32 and (i // tp) // 64 > 148)
+                       if L.load().ffn_int4_set_batched_kernel(-1) == 0 or (L.load().ffn_int4_set_batched_kernel(-1) == 2 and m > 16 and 2 * ((i // tp) // 64) >= 148)
                        else "batched pair (mma.sync bf16)"),
             "exchange": ("none (one GPU)" if world == 1 else "in-kernel tagged-word exchange over NVLink peer memory"
                          if not use_nccl else "comparison variant: NCCL all-reduce of the BF16 output after the kernel"),

@@ -271,10 +271,21 @@ __global__ void __launch_bounds__(kMmaThreads) down_mma_kernel(const MmaParams P
         __syncthreads();
         if (!last_arrival) return;
         __threadfence();
+        /* every load of an element is issued before the first add, and four elements go together: a loop
+         * of load-then-add over a run-time split count serialises the trips to L2 (224 of them per
+         * thread at 64 tokens).  Measured against a split-outer form with eight elements in flight:
+         * this one is the faster (185.6 vs 204.0 us per FFN at 64 tokens, 72.5 vs 74.5 at 16). */
+#pragma unroll 4
         for (int i = threadIdx.x; i < kMmaRows * P.M; i += kMmaThreads) {
             const int r = i % kMmaRows, m = i / kMmaRows;
+            float v[kMmaMaxSplits];
+#pragma unroll
+            for (int q = 0; q < kMmaMaxSplits; ++q)
+                v[q] = q < P.splits ? __ldcg(P.partial + ((size_t)q * P.M + m) * P.N + row0 + r) : 0.0f;
             float y = 0.0f;
-            for (int q = 0; q < P.splits; ++q) y += __ldcg(P.partial + ((size_t)q * P.M + m) * P.N + row0 + r);
+#pragma unroll
+            for (int q = 0; q < kMmaMaxSplits; ++q)
+                if (q < P.splits) y += v[q];
             red[(size_t)r * ldr + m] = y;
         }
         /* each thread reads back only what it wrote to `red` itself: no barrier needed */

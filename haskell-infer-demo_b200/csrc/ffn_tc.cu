@@ -112,16 +112,13 @@ struct TcParams {
     unsigned long long *const *peer_slots;
     unsigned *tp_seq;
     unsigned *status;         /* word 3 of the device's synchronisation words */
-    long long *trace;         /* debugging aid (ffn_int4_debug_trace): CTA 0 stamps the first 32 groups of each role */
+    long long *trace;         /* debugging aid (ffn_int4_debug_trace): CTA 0 stamps the first 64 groups of each role */
 };
 
-/* role r, group gi -> trace[r * 32 + gi], SM clock cycles */
+/* role r, group gi -> trace[r * 64 + gi], SM clock cycles; role 7 holds single events (0: epilogue starts a
+ * unit, 1: its group loop is over, 2: the unit's output is written) */
 __device__ __forceinline__ void tc_stamp(const TcParams &P, int role, uint32_t gi) {
-    if (P.trace && blockIdx.x == 0 && gi < 32u) {
-        long long t;
-        t = clock64();
-        P.trace[role * 32 + gi] = t;
-    }
+    if (P.trace && blockIdx.x == 0 && gi < 64u) P.trace[role * 64 + gi] = clock64();
 }
 
 /* ---- tcgen05 wrappers ------------------------------------------------------------------------ */
@@ -462,6 +459,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) ffn_tc_kernel(const __grid_cons
 #pragma unroll
             for (int c = 0; c < NPAD; ++c) acc[c] = 0.0f;
             ok = __all_sync(~0u, ok && !sm->abort_flag);
+            if (L == 0 && u == (int)blockIdx.x) tc_stamp(P, 7, 0);
             /* The scales of this row come through shared memory, 64 groups at a time: a global load per
              * group would put its latency (hundreds of cycles) into every turn of the loop below.  A
              * thread reads back only what it wrote itself, so no barrier is needed. */
@@ -503,6 +501,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) ffn_tc_kernel(const __grid_cons
                     if (L == 0) tc_stamp(P, 6, gi);
                 }
             }
+            if (L == 0 && u == (int)blockIdx.x) tc_stamp(P, 7, 1);
             /* every epilogue thread passes the same barriers below whatever happened above */
             if (PAIRS) {
 #pragma unroll
@@ -553,17 +552,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) ffn_tc_kernel(const __grid_cons
                     if (finish) {
                         /* the last of the row block's K splits to arrive adds them in split order */
                         __threadfence();
+                        /* split by split, all tokens of a split together: the loads of one split are
+                         * independent of one another, so they are in flight together (a loop of
+                         * load-then-add per token serialises the trips to L2: 190 of them took 67 us) */
 #pragma unroll
-                        for (int m = 0; m < NPAD; ++m)
-                            if (m < P.M) {
-                                float y = 0.0f;
-                                for (int q = 0; q < P.splits; ++q) y += __ldcg(P.partial + ((size_t)q * P.M + m) * P.N + grow);
-                                acc[m] = y;
-                            }
+                        for (int m = 0; m < NPAD; ++m) acc[m] = 0.0f;
+                        for (int q = 0; q < P.splits; ++q) {
+                            const float *from = P.partial + (size_t)q * P.M * P.N + grow;
+#pragma unroll
+                            for (int m = 0; m < NPAD; ++m)
+                                if (m < P.M) acc[m] += __ldcg(from + (size_t)m * P.N);
+                        }
                     }
                 }
                 if (finish && ok) tc_down_output<NPAD>(P, sm, acc, grow, seq);
             }
+            if (L == 0 && u == (int)blockIdx.x) tc_stamp(P, 7, 2);
         }
     }
     tc_fence_before();
@@ -607,11 +611,12 @@ int tc_set_mode(int mode) {
     if (mode >= 0 && mode <= 2) g_tc_mode = mode;
     return old;
 }
-/* Measured on B200 (5120 x 17408): faster than the mma.sync pair above 32 tokens when the gate/up launch
- * has more units than SMs (165 vs 210 us at 64 tokens); a tie on tensor-parallel slices (150 vs 150 us
- * at TP=2, 138 vs 137 at TP=4), which therefore stay with the mma.sync pair. */
+/* Measured on B200 (5120 x 17408, us per FFN, tcgen05 vs mma.sync pair): 8 tokens 79 vs 56, 16: 82 vs 73,
+ * 24: 91 vs 93, 32: 93 vs 96, 48: 107 vs 177, 64: 123 vs 186; on TP=2 slices 32: 75 vs 77, 64: 114 vs 132.
+ * So: more than 16 tokens, and enough gate/up units (intermediate size / 64) to occupy half the SMs -
+ * smaller slices (TP=8 of that layer: 34 units) stay with the mma.sync pair. */
 static bool tc_wanted(int tokens, int I, int sm_count) {
-    return g_tc_mode == 0 || (g_tc_mode == 2 && tokens > 32 && I / 64 > sm_count);
+    return g_tc_mode == 0 || (g_tc_mode == 2 && tokens > 16 && 2 * (I / 64) >= sm_count);
 }
 
 /* The driver's tensor-map encoder, through the runtime (no link against the driver library). */
@@ -753,7 +758,7 @@ int tc_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *laye
     B.stages = A.stages;
     B.out = (uint16_t *)layer_out; B.residual = (uint16_t *)residual;
     B.partial = (float *)(sc.base + counters + xt_bytes + at_bytes); B.arrivals = (unsigned *)sc.base;
-    B.tp = 1; B.status = status;
+    B.tp = 1; B.status = status; B.trace = A.trace ? A.trace + 512 : nullptr;
     if (tp && tp->tp > 1) {
         if (tokens * H > tp->slot_stride) return fail(FFN_ERR_CONFIG, "tcgen05 FFN: %d tokens exceed the exchange buffer", tokens);
         A.tp_seq = tp->seq;

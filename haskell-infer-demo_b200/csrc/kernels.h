@@ -145,7 +145,7 @@ bool kmajor_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin
 /* ffn_mma.cu: the tensor-core path for 3..64 tokens (two launches: gate/up + SiLU*up, down + reduce). */
 /* ffn_tc.cu: the same contract on tcgen05 tensor cores (accumulators in tensor memory); batched_ffn_launch
  * tries it first and falls back to the mma.sync pair for shapes it does not take.  tc_set_mode: 0 always,
- * 1 never, 2 (default) where it measured faster (more than 32 tokens and more gate/up units than SMs);
+ * 1 never, 2 (default) where it measured faster (more than 16 tokens, gate/up units for half the SMs);
  * returns the previous mode. */
 int tc_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                   const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual, unsigned *status);

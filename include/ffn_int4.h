@@ -89,8 +89,8 @@ int ffn_int4_describe_gemm_plan(int m, int n, int k, int sm_count, int smem_opti
 
 /* Debugging aid: when given a device buffer of 16 int64 per SM (16 x 148 on B200), every CTA of every
  * later decode-kernel launch writes global-timer stamps (ns) of its pipeline events to its own 16
- * words; the tcgen05 pair's gate/up launch instead has CTA 0 write SM-clock stamps of its roles' first
- * 32 groups to words [role * 32 + group] (NULL switches it off).  No counterpart in the
+ * words; the tcgen05 pair instead has CTA 0 write SM-clock stamps of its roles' first 64 groups to words
+ * [role * 64 + group] (gate/up launch) and [512 + role * 64 + group] (down launch).  NULL switches it off.  No counterpart in the
  * reference (its profiler times whole regions with events, csrc/profile.cu:114-144). */
 void ffn_int4_debug_trace(void *device_buffer);
 
@@ -263,9 +263,9 @@ int ffn_int4_set_decode_kernel(int which);
  * (tcgen05.mma with FP32 accumulators and the converted BF16 operand in tensor memory, packed INT4 rows
  * brought in by tiled TMA loads), falling back to the mma.sync pair for shapes it does not take (hidden
  * size not a multiple of 128, intermediate size not a multiple of 64); 2 (default) the tcgen05 pair
- * where it measured faster on B200 - more than 32 tokens and more gate/up units (intermediate size / 64)
- * than SMs: 165 vs 211 us at 64 tokens on the 5120 x 17408 layer - and the mma.sync pair elsewhere
- * (tensor-parallel slices measured a tie).  Same arithmetic in both: exact codes times BF16
+ * where it measured faster on B200 - more than 16 tokens and enough gate/up units (intermediate size / 64)
+ * for half the SMs: 123 vs 186 us at 64 tokens, 93 vs 96 at 32 on the 5120 x 17408 layer, 114 vs 132 at
+ * 64 tokens on its TP=2 slice - and the mma.sync pair elsewhere (73 vs 82 us at 16 tokens).  Same arithmetic in both: exact codes times BF16
  * activations summed in FP32 per 128-wide group, times the group's scale (the reference's tiled
  * kernel, csrc/kernels/gemm_quant.cu:134-147).  Returns the previous setting; any other value queries. */
 int ffn_int4_set_batched_kernel(int which);

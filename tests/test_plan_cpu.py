@@ -55,7 +55,7 @@ def test_headline_shape_uses_all_of_shared_memory():
 @pytest.mark.parametrize("hidden,inter,tp", [(5120, 17408, 1), (5120, 17408, 8), (1024, 3072, 1), (2560, 9728, 2)])
 def test_batched_plan(tokens, hidden, inter, tp):
     local = inter // tp
-    assert plan(tokens, hidden, local)["kernel"] == ("tcgen05_pair" if tokens > 32 and local // 64 > SMS else "mma_pair")   # the default choice
+    assert plan(tokens, hidden, local)["kernel"] == ("tcgen05_pair" if tokens > 16 and 2 * (local // 64) >= SMS else "mma_pair")   # the default choice
     old = L.load().ffn_int4_set_batched_kernel(1)
     try:
         p = plan(tokens, hidden, local)
