@@ -72,7 +72,7 @@ constexpr int kTcTeamWarps = kTcConvWarps / kTcConvTeams;
 constexpr int kTcProducerWarp = kTcEpiWarps, kTcFirstConvWarp = kTcEpiWarps + 1, kTcFirstMmaWarp = kTcFirstConvWarp + kTcConvWarps;
 constexpr int kTcThreads = (kTcFirstMmaWarp + kTcMmaWarps) * 32;        /* 544 */
 constexpr int kTcMaxSplits = 8;
-constexpr int kTcHeader = 5120;               /* barriers, flags, the 64 x 17 exchange buffer of the pairs epilogue */
+constexpr int kTcHeader = 9216;               /* barriers, flags, the two 64 x 17 hand-over buffers of the pairs epilogue */
 constexpr int kTcScaleGroups = 64;            /* groups of scales the epilogue keeps in shared memory at a time: [64][128 rows] bf16 */
 constexpr int kTcScaleBytes = kTcScaleGroups * kTcRows * 2;
 constexpr int kTcBoxRows = 64;                /* rows per TMA box: the gate half and the up half of a unit are separate row ranges */
@@ -89,7 +89,7 @@ struct TcSmem {
     uint32_t tmem_base;
     int abort_flag;
     int last_arrival;
-    float ex[64 * 17];
+    float ex_gate[64 * 17], ex_up[64 * 17]; /* the pairs epilogue's hand-over, 16 tokens at a time */
 };
 static_assert(sizeof(TcSmem) <= kTcHeader, "header");
 
@@ -504,22 +504,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) ffn_tc_kernel(const __grid_cons
             if (L == 0 && u == (int)blockIdx.x) tc_stamp(P, 7, 1);
             /* every epilogue thread passes the same barriers below whatever happened above */
             if (PAIRS) {
+                /* SiLU(gate) * up, 16 tokens at a time: gate rows sit in lanes 0-63, up rows in lanes 64-127,
+                 * so both halves hand their sums over through shared memory and ALL four warps then finish
+                 * pairs - thread L takes pair L mod 64 and tokens 8 * (L / 64) .. + 7 of the batch. */
+                const int pr = L & 63, half = L >> 6;
+                const int p = t.row_a + pr; /* this rank's gate/up pair = column of the down projection */
+                const int kb = p >> 6, piece = (p >> 3) & 7; /* K block of 64 columns of the down projection; 16-byte piece in it */
+                uint8_t *tile = P.act_t + (size_t)kb * NPAD * 128 + tc_permute8(p & 7) * 2;
 #pragma unroll
                 for (int t16 = 0; t16 < NT; ++t16) {
-                    if (L >= 64) {
+                    float *mine = (L < 64 ? sm->ex_gate : sm->ex_up) + pr * 17;
 #pragma unroll
-                        for (int c = 0; c < 16; ++c) sm->ex[(L - 64) * 17 + c] = acc[t16 * 16 + c];
-                    }
+                    for (int c = 0; c < 16; ++c) mine[c] = acc[t16 * 16 + c];
                     epi_bar();
-                    if (L < 64 && ok) {
-                        const int p = t.row_a + L; /* this rank's gate/up pair = column of the down projection */
-                        const int kb = p >> 6, piece = (p >> 3) & 7; /* K block of 64 columns of the down projection; 16-byte piece in it */
-                        uint8_t *tile = P.act_t + (size_t)kb * NPAD * 128 + tc_permute8(p & 7) * 2;
+                    if (ok) {
 #pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            const int m = t16 * 16 + c;
+                        for (int c8 = 0; c8 < 8; ++c8) {
+                            const int c = half * 8 + c8, m = t16 * 16 + c;
                             if (m < P.M) {
-                                const uint16_t a = f32_to_bf16_bits(silu_mul(round_bf16(acc[m]), round_bf16(sm->ex[L * 17 + c])));
+                                const uint16_t a = f32_to_bf16_bits(silu_mul(round_bf16(sm->ex_gate[pr * 17 + c]), round_bf16(sm->ex_up[pr * 17 + c])));
                                 P.act[(size_t)m * P.N + p] = a;
                                 *(uint16_t *)(tile + tc_tile_offset(m, piece)) = a;
                             }
