@@ -15,13 +15,14 @@
  *   warps 0-3   epilogue: tcgen05.ld of a finished group (warp w reads lanes 32w..32w+31: thread =
  *               weight row), scale, accumulate; at the end of a unit SiLU(gate)*up or the split-K
  *               hand-over and the output / cross-rank exchange.
- *   warp 4      producer (one thread): per stage two tiled TMA loads (cp.async.bulk.tensor.2d, 64 rows x 128 bytes of
- *               packed codes each, 128-byte swizzle so the conversion warps read without bank conflicts)
- *               and one bulk copy of the stage's slice of the activations, completion on mbarriers.
+ *   warp 4      producer (one thread): per stage two tiled TMA loads (cp.async.bulk.tensor.2d, 64 rows x
+ *               128 bytes of packed codes each, 128-byte swizzle so the conversion warps read without
+ *               bank conflicts) and one bulk copy of the stage's slice of the activations, completion
+ *               on mbarriers; the ring is as deep as shared memory allows (4 to 8 stages).
  *   warps 5-12  conversion: INT4 codes of the stage -> exact BF16 codes, written from registers straight
  *               into tensor memory (tcgen05.st), where the MMA reads its A operand: no shared-memory
  *               copy of the 4x larger BF16 tile, so shared memory is all ring.  Two teams of four
- *               warps work on two groups at a time.
+ *               warps (one warp per tensor-memory quadrant) take alternate stages.
  *   warps 13-16 one thread each issues the MMAs (8 per group, K = 16, A from tensor memory, B = the
  *               stage's activation slice in shared memory) of every fourth group and commits them to
  *               the mbarriers that publish the accumulator and free the operands; warp 13 also
@@ -34,9 +35,8 @@
  * 128-byte row at (n/8)*1024 + (n%8)*128 whose 16-byte piece c (8 values of K) sits at piece c ^ (n%8),
  * the 8 values in the order (0,4),(1,5),(2,6),(3,7) - the order in which one lop3 + one packed subtract
  * deliver the codes of a 32-bit word.  A stage's slice is then one contiguous bulk copy and already
- * the MMA's swizzled B-operand layout.  A small pre-pass writes the
- * input that way; the gate/up epilogue writes act that way for the down launch (and in natural order
- * for the caller).
+ * the MMA's swizzled B-operand layout.  A small pre-pass writes the input that way; the gate/up
+ * epilogue writes act that way for the down launch (and in natural order for the caller).
  *
  * Two launches per FFN, as the mma.sync pair (ffn_mma.cu): gate/up + SiLU*up, then down with K split
  * over CTAs (FP32 partial sums through global memory, added in split order by the last to arrive) and
