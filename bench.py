@@ -22,6 +22,12 @@ timed, compared with the oracle at the stated bars (relative L2 <= 5e-3, max-abs
 BF16 ulp)); a failed comparison makes the run exit non-zero.  `cpu_baseline` times the CPU oracle
 chain on this box's host cores on a bounded sample.
 
+Comparison variants and side measurements (none of them the headline): --kmajor (the persistent decode
+kernel over k-major copies of the down projection), --batched-kernel tcgen05|mma.sync (which pair serves
+3..64 tokens), --no-overlap (launches without the dependent-launch attribute), --exchange nccl (N > 1:
+the same kernel per rank followed by an NCCL all-reduce), --gemv N,K (one INT4 GEMM call of that
+shape), --profile-range (the timed step between cudaProfilerStart/Stop, for a launch list under ncu).
+
 --impl reference times the reference's own CPU arithmetic for the path on the host cores (the
 reference's compiled dequantizer from oracle/_ref when present, else the oracle's restatement;
 matmuls in PyTorch on all host threads) and prints the same JSON line with "impl": "reference".
