@@ -186,6 +186,11 @@ int ffn_int4_set_batched_kernel(int which) {
     return tc_set_mode(which);
 }
 
+long long ffn_int4_tile_order_offset(int token, int k, int padded_tokens) {
+    if (token < 0 || k < 0 || padded_tokens < 16 || padded_tokens % 16 || token >= padded_tokens) return -1;
+    return tc_tile_order_offset(token, k, padded_tokens);
+}
+
 int ffn_int4_set_launch_overlap(int on) {
     if (on != 0 && on != 1) {
         const int current = fused_set_launch_overlap(1);

@@ -776,6 +776,13 @@ int tc_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *laye
     }
 }
 
+/* Byte offset of activation (token, k) in the tile order the tcgen05 pair reads (host arithmetic: the
+ * layout's definition for tests and for an engine that wants to write activations that way itself). */
+long long tc_tile_order_offset(int token, int k, int npad) {
+    const int block = k >> 6, piece = (k >> 3) & 7, e = k & 7;
+    return (long long)block * npad * 128 + tc_tile_offset(token, piece) + (((e & 3) << 1) | (e >> 2)) * 2;
+}
+
 /* 3..64 tokens: the tcgen05 pair where it takes the shape, else the mma.sync pair. */
 int batched_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                        const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual, unsigned *status) {

@@ -153,6 +153,7 @@ int batched_ffn_launch(cudaStream_t stream, const void *normed, void *act, void 
                        const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual, unsigned *status);
 bool tc_describe_plan(int tokens, int H, int I, int sm_count, int smem_optin, char *out, size_t out_bytes);
 int tc_set_mode(int mode);
+long long tc_tile_order_offset(int token, int k, int npad);
 void tc_reset_sync();
 int mma_ffn_launch(cudaStream_t stream, const void *normed, void *act, void *layer_out,
                    const FfnMlpWeights *w, int tokens, int H, int I, const FusedTp *tp, void *residual, unsigned *status);

@@ -113,6 +113,8 @@ def _declare(lib):
     lib.ffn_quant_manifest_free.restype = None
     lib.ffn_host_free.argtypes = [vp]
     lib.ffn_host_free.restype = None
+    lib.ffn_int4_tile_order_offset.argtypes = [ci, ci, ci]
+    lib.ffn_int4_tile_order_offset.restype = ctypes.c_longlong
     lib.ffn_int4_debug_trace.argtypes = [vp]
     lib.ffn_int4_debug_trace.restype = None
     for name, args in sigs.items():

@@ -270,6 +270,15 @@ int ffn_int4_set_decode_kernel(int which);
  * kernel, csrc/kernels/gemm_quant.cu:134-147).  Returns the previous setting; any other value queries. */
 int ffn_int4_set_batched_kernel(int which);
 
+/* The layout the tcgen05 pair reads activations in ("tile order"), as arithmetic: byte offset of element
+ * (token, k) of a bf16 [tokens][K] matrix whose token count is padded to `padded_tokens` (a multiple of
+ * 16).  K runs in blocks of 64 values; inside a block a token owns a 128-byte row at
+ * (token / 8) * 1024 + (token % 8) * 128, whose 16-byte piece c sits at piece c ^ (token % 8) (the
+ * 128-byte swizzle of the MMA's shared-memory operand), the 8 values of a piece in the order
+ * (0,4),(1,5),(2,6),(3,7).  -1 for arguments out of range.  Pure host arithmetic, no counterpart in
+ * the reference. */
+long long ffn_int4_tile_order_offset(int token, int k, int padded_tokens);
+
 /* Overlap of consecutive FFN launches in one stream (default 1, on).  The fused FFN kernel is launched
  * with the programmatic-dependent-launch attribute: the next launch's CTAs are scheduled onto SMs as
  * this launch's CTAs leave them, set up their barriers and start the first copies of the weight stream,

@@ -100,3 +100,28 @@ def test_smaller_shared_memory_means_fewer_stages_or_another_kernel():
     small = plan(1, 5120, 17408, smem=170000)
     assert small["kernel"] == "fused" and small["stages"] < big["stages"]
     assert plan(1, 5120, 17408, smem=100 * 1024)["kernel"] != "fused"
+
+
+@pytest.mark.parametrize("padded", [16, 32, 48, 64])
+def test_tile_order_is_a_bijection_with_the_documented_structure(padded):
+    """The activation layout of the tcgen05 pair (host arithmetic): every (token, k) of a [padded, K] bf16
+    matrix gets its own 2-byte slot in [0, padded * K * 2); a 64-wide K block of all tokens is one
+    contiguous padded * 128-byte slice (what one bulk copy per stage brings in); a token's 8 consecutive
+    values of K share one 16-byte piece in the order (0,4),(1,5),(2,6),(3,7); pieces are swizzled by
+    token & 7 inside the token's 128-byte row."""
+    lib = L.load()
+    K = 256
+    off = [[lib.ffn_int4_tile_order_offset(n, k, padded) for k in range(K)] for n in range(padded)]
+    flat = sorted(o for row in off for o in row)
+    assert flat == list(range(0, padded * K * 2, 2))
+    for n in (0, 5, padded - 1):
+        for k0 in range(0, K, 64):
+            block = [off[n][k] for k in range(k0, k0 + 64)]
+            assert min(block) // (padded * 128) == k0 // 64 == max(block) // (padded * 128)          # the K block's slice
+            row = (k0 // 64) * padded * 128 + (n // 8) * 1024 + (n % 8) * 128
+            assert all(row <= o < row + 128 for o in block)                                          # the token's row in it
+            for c in range(8):
+                piece = [off[n][k0 + 8 * c + e] for e in range(8)]
+                base = row + ((c ^ (n % 8)) << 4)
+                assert [p - base for p in piece] == [0, 4, 8, 12, 2, 6, 10, 14]                      # (0,4),(1,5),(2,6),(3,7)
+    assert lib.ffn_int4_tile_order_offset(padded, 0, padded) == -1 and lib.ffn_int4_tile_order_offset(0, 0, 24) == -1
