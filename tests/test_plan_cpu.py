@@ -125,3 +125,16 @@ def test_tile_order_is_a_bijection_with_the_documented_structure(padded):
                 base = row + ((c ^ (n % 8)) << 4)
                 assert [p - base for p in piece] == [0, 4, 8, 12, 2, 6, 10, 14]                      # (0,4),(1,5),(2,6),(3,7)
     assert lib.ffn_int4_tile_order_offset(padded, 0, padded) == -1 and lib.ffn_int4_tile_order_offset(0, 0, 24) == -1
+
+
+def test_timeline_tool_imports_and_refuses_without_a_gpu(monkeypatch):
+    import sys
+
+    import torch
+
+    import haskell_infer_demo_b200.trace as trace
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present: the tool would run")
+    monkeypatch.setattr(sys, "argv", ["trace", "decode"])
+    with pytest.raises(SystemExit):
+        trace.main()
